@@ -1,0 +1,24 @@
+// Host-side interface of the tile-sparse linear (packed weight object + launch).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+namespace et {
+
+struct TileWeight;
+
+// Validates the BSR arrays (host pointers), re-packs them for the kernel and uploads.
+// nb_override > 0 forces the block-rows-per-CTA choice (tests); 0 picks it from size_hint.
+int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, const half* data,
+                     const int* row_ptr, const int* row_offset, const half* bias, int nb_override);
+void tile_weight_free(TileWeight* w);
+int tile_weight_set_bias_device(TileWeight* w, const half* bias_dev, cudaStream_t st);
+int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st);
+// Reads and clears the device error word (0 = no bounded wait gave up). Synchronises.
+int tile_weight_error(const TileWeight* w, int* code);
+void tile_weight_info(const TileWeight* w, int* info6);
+int tile_spmm_raw(half* Y, const half* X, const int* row_ptr, const int* row_offset, const half* data,
+                  int M, int N, int K, const half* bias, int gelu, cudaStream_t st);
+void tile_spmm_cache_clear();
+
+}  // namespace et
