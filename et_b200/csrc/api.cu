@@ -1,10 +1,8 @@
 // extern "C" entry points that are thin adapters over the host-side C++ of this library.
 #include "common.h"
+#include "handles.h"
 #include "tile_gemm.h"
 
-struct et_tile_weight {
-    et::TileWeight* w;
-};
 
 extern "C" int et_tile_weight_create(et_tile_weight** out, int in_feat, int out_feat, int size,
                                      int ntile, const void* data_host, const int* row_ptr_host,

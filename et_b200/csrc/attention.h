@@ -1,0 +1,19 @@
+// Host-side launchers of the attention kernels.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+namespace et {
+
+// General form. Q/K share q_pitch; scores != null replaces Q K^T by precomputed, already scaled
+// scores [batch][nhead][L][L] (equal-length sequences only). cu_seqlens (device, batch+1 ints) or, when
+// null, `batch` sequences of uniform_len tokens each. valid_lens (device) limits the keys per sequence.
+int attention_launch(half* Z, const half* Q, const half* K, const half* V, const half* scores,
+                     int q_pitch, int v_pitch, const int* qk_head_ptr, const int* v_col_id,
+                     const int* v_head_ptr, const half* mask, int mask_ld, const int* cu_seqlens,
+                     const int* valid_lens, int batch, int uniform_len, int total_tokens, int d_model,
+                     int nhead, cudaStream_t st);
+int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, int d_model, int nhead,
+                     cudaStream_t st);
+
+}  // namespace et

@@ -1,0 +1,418 @@
+// Host-side layer objects: the row-pruned linear and the three encoder-layer variants, plus their
+// C-ABI entry points. Replaces encoder/Linear.cu:60-91 (Linear_row), encoder/encoder.h:7-134 and
+// encoder/encoder.cu:4-149 (Encoder_base / Encoder_tile / Encoder_prune / Encoder_length) of the reference.
+//
+// Differences from the reference by design: one stream, no host synchronisation inside run(), no cuBLAS;
+// a batch of packed variable-length sequences is a first-class input (run_batch); every failure is a
+// status code instead of exit(1).
+#include <algorithm>
+#include <memory>
+#include <vector>
+#include "attention.h"
+#include "common.h"
+#include "formats.h"
+#include "handles.h"
+#include "tile_gemm.h"
+
+
+namespace et {
+
+// ------------------------------------------------------------------------------ row-pruned linear
+// Only `row_id_size` output features survive (sorted original indices in row_id); the weight is the
+// compact [row_id_size x in_feat] matrix. Output is [tokens x nrow] with nrow = row_id_size rounded up
+// to 16 (zero columns beyond row_id_size), the pitch every consumer uses. The contraction runs on the
+// tile kernel with every tile kept.
+struct RowWeight {
+    int in_feat = 0, out_feat = 0, nhead = 0, row_id_size = 0, nrow = 0;
+    TileWeight* tw = nullptr;
+    int* d_row_id = nullptr;
+    int* d_head_ptr = nullptr;
+    std::vector<int> h_head_ptr;
+    ~RowWeight() {
+        tile_weight_free(tw);
+        cudaFree(d_row_id);
+        cudaFree(d_head_ptr);
+    }
+};
+
+static int dense_to_tiles(const half* weight, int rows, int K, std::vector<half>& data,
+                          std::vector<int>& row_ptr, std::vector<int>& row_offset) {
+    const int nrow = (rows + 15) / 16 * 16;
+    const int brs = nrow / 16, bcs = K / 16;
+    data.assign((size_t)brs * bcs * 256, __float2half(0.f));
+    row_ptr.resize(brs + 1);
+    row_offset.resize((size_t)brs * bcs);
+    for (int r = 0; r < brs; ++r) {
+        row_ptr[r] = r * bcs;
+        for (int c = 0; c < bcs; ++c) {
+            const size_t i = (size_t)r * bcs + c;
+            row_offset[i] = c * 16;
+            for (int n = 0; n < 16 && 16 * r + n < rows; ++n)
+                for (int k = 0; k < 16; ++k)
+                    data[i * 256 + n * 16 + k] = weight[(size_t)(16 * r + n) * K + 16 * c + k];
+        }
+    }
+    row_ptr[brs] = brs * bcs;
+    return nrow;
+}
+
+static int row_weight_create(RowWeight** out, int in_feat, int out_feat, int size, const half* weight,
+                             const int* row_id, int row_id_size, const half* bias, int nhead) {
+    if (!out) return fail(ET_ERR_INVALID, "row weight: null output");
+    *out = nullptr;
+    if (in_feat <= 0 || in_feat % 16 || out_feat <= 0 || row_id_size <= 0 || row_id_size > out_feat)
+        return fail(ET_ERR_INVALID, "row weight: bad dimensions (in_feat must be a multiple of 16)");
+    if (!weight || !row_id) return fail(ET_ERR_INVALID, "row weight: null array");
+    if (nhead <= 0 || out_feat % nhead) return fail(ET_ERR_INVALID, "row weight: out_feat not divisible by nhead");
+    for (int i = 0; i < row_id_size; ++i)
+        if (row_id[i] < 0 || row_id[i] >= out_feat || (i && row_id[i] <= row_id[i - 1]))
+            return fail(ET_ERR_INVALID, "row weight: row_id must be strictly ascending inside [0, out_feat)");
+    auto w = std::make_unique<RowWeight>();
+    w->in_feat = in_feat; w->out_feat = out_feat; w->nhead = nhead; w->row_id_size = row_id_size;
+    std::vector<half> data;
+    std::vector<int> rp, ro;
+    w->nrow = dense_to_tiles(weight, row_id_size, in_feat, data, rp, ro);
+    std::vector<half> pbias(w->nrow, __float2half(0.f));
+    if (bias) std::copy(bias, bias + row_id_size, pbias.begin());
+    int rc = tile_weight_pack(&w->tw, in_feat, w->nrow, size, (long)ro.size(), data.data(), rp.data(),
+                              ro.data(), pbias.data(), 0);
+    if (rc) return rc;
+    build_head_ptr(row_id, row_id_size, nhead, out_feat, w->h_head_ptr);
+    if (cudaMalloc(&w->d_row_id, sizeof(int) * row_id_size) != cudaSuccess ||
+        cudaMalloc(&w->d_head_ptr, sizeof(int) * (nhead + 1)) != cudaSuccess)
+        return fail(ET_ERR_CUDA, "row weight: cudaMalloc failed");
+    cudaMemcpy(w->d_row_id, row_id, sizeof(int) * row_id_size, cudaMemcpyHostToDevice);
+    cudaMemcpy(w->d_head_ptr, w->h_head_ptr.data(), sizeof(int) * (nhead + 1), cudaMemcpyHostToDevice);
+    *out = w.release();
+    return ET_OK;
+}
+
+// ------------------------------------------------------------------------------ encoder layer
+enum EncoderKind { kTile = 0, kPrune = 1, kLength = 2, kPruneQKV = 3 };
+
+struct Encoder {
+    int kind = kTile, d_model = 0, seq_len = 0, nheads = 0, d_ff = 0;
+    half* buffer = nullptr;  // caller-owned scratch for run(): buffer_num * seq_len * d_model halfs (+ scores)
+    TileWeight* lin[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v o mlp1 mlp2
+    RowWeight* rq = nullptr; RowWeight* rk = nullptr; RowWeight* rv = nullptr;
+    half* d_ln[4] = {nullptr, nullptr, nullptr, nullptr};  // gamma1 beta1 gamma2 beta2
+    half* d_mask = nullptr;                                // [seq_len x seq_len] additive, may be null
+    int* d_lens = nullptr; int lens_cap = 0;               // cu_seqlens (batch+1) then valid_lens (batch)
+    bool materialize_scores = false;
+    ~Encoder() {
+        for (auto* t : lin) tile_weight_free(t);
+        delete rq; delete rk; delete rv;
+        for (auto* p : d_ln) cudaFree(p);
+        cudaFree(d_mask);
+        cudaFree(d_lens);
+    }
+};
+
+static int upload_half(half** dst, const half* src_host, size_t n) {
+    if (cudaMalloc(dst, n * sizeof(half)) != cudaSuccess) return fail(ET_ERR_CUDA, "encoder: cudaMalloc failed");
+    return cuda_status(cudaMemcpy(*dst, src_host, n * sizeof(half), cudaMemcpyHostToDevice), "encoder: upload");
+}
+
+static int encoder_common(Encoder* e, int d_model, int seq_len, int nheads, half* buffer,
+                          const half* g1, const half* b1, const half* g2, const half* b2, const half* mask) {
+    if (d_model <= 0 || seq_len <= 0 || nheads <= 0 || d_model % nheads) return fail(ET_ERR_INVALID, "encoder: bad dimensions");
+    if (!g1 || !b1 || !g2 || !b2) return fail(ET_ERR_INVALID, "encoder: null LayerNorm parameter");
+    e->d_model = d_model; e->seq_len = seq_len; e->nheads = nheads; e->buffer = buffer;
+    const half* src[4] = {g1, b1, g2, b2};
+    for (int i = 0; i < 4; ++i) {
+        int rc = upload_half(&e->d_ln[i], src[i], d_model);
+        if (rc) return rc;
+    }
+    if (mask) return upload_half(&e->d_mask, mask, (size_t)seq_len * seq_len);
+    return ET_OK;
+}
+
+// One layer over `T` packed tokens (op order of encoder/encoder.cu:20-45). scratch holds 5*T*d_model halfs:
+// [0] Q then the attention-output projection / first LayerNorm result, [1] K, [2] V, [3] attention output,
+// [1..4] the T x d_ff hidden activations; scores (materialised variant) follow at 5*T*d_model.
+static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch, int T, const int* cu_seqlens,
+                           const int* valid_lens, int batch, int uniform_len, cudaStream_t st) {
+    const size_t td = (size_t)T * e->d_model;
+    half* b0 = scratch; half* b1 = scratch + td; half* b2 = scratch + 2 * td; half* b3 = scratch + 3 * td;
+    int rc;
+    int q_pitch = e->d_model, v_pitch = e->d_model;
+    const int *qk_hp = nullptr, *v_hp = nullptr, *v_id = nullptr;
+    if (e->kind == kPruneQKV) {
+        if ((rc = tile_linear_run(e->rq->tw, b0, in, T, 0, st))) return rc;
+        if ((rc = tile_linear_run(e->rk->tw, b1, in, T, 0, st))) return rc;
+        q_pitch = e->rq->nrow; qk_hp = e->rq->d_head_ptr;
+    } else {
+        if ((rc = tile_linear_run(e->lin[0], b0, in, T, 0, st))) return rc;
+        if ((rc = tile_linear_run(e->lin[1], b1, in, T, 0, st))) return rc;
+    }
+    if (e->kind == kPrune || e->kind == kPruneQKV) {
+        if ((rc = tile_linear_run(e->rv->tw, b2, in, T, 0, st))) return rc;
+        v_pitch = e->rv->nrow; v_hp = e->rv->d_head_ptr; v_id = e->rv->d_row_id;
+    } else {
+        if ((rc = tile_linear_run(e->lin[2], b2, in, T, 0, st))) return rc;
+    }
+    const half* scores = nullptr;
+    if (e->kind == kLength && e->materialize_scores && !cu_seqlens) {
+        half* sbuf = scratch + 5 * td;
+        if ((rc = qk_scores_launch(sbuf, b0, b1, batch, uniform_len, e->d_model, e->nheads, st))) return rc;
+        scores = sbuf;
+    }
+    if ((rc = attention_launch(b3, b0, b1, b2, scores, q_pitch, v_pitch, qk_hp, v_id, v_hp, e->d_mask, e->seq_len,
+                               cu_seqlens, valid_lens, batch, uniform_len, T, e->d_model, e->nheads, st)))
+        return rc;
+    if ((rc = tile_linear_run(e->lin[3], b0, b3, T, 0, st))) return rc;
+    if ((rc = et_skip_layernorm(b0, in, e->d_ln[0], e->d_ln[1], T, e->d_model, st))) return rc;
+    if ((rc = tile_linear_run(e->lin[4], b1, b0, T, 1, st))) return rc;
+    if ((rc = tile_linear_run(e->lin[5], out, b1, T, 0, st))) return rc;
+    return et_skip_layernorm(out, b0, e->d_ln[2], e->d_ln[3], T, e->d_model, st);
+}
+
+}  // namespace et
+
+using et::Encoder;
+using et::RowWeight;
+
+struct et_row_weight {
+    RowWeight* w;
+};
+struct et_encoder {
+    Encoder* e;
+};
+
+extern "C" {
+
+int et_row_weight_create(et_row_weight** out, int in_feat, int out_feat, int size, const void* weight_host,
+                         const int* row_id_host, int row_id_size, const void* bias_host, int nhead) {
+    ET_REQUIRE(out, "et_row_weight_create: null output");
+    *out = nullptr;
+    RowWeight* w = nullptr;
+    int rc = et::row_weight_create(&w, in_feat, out_feat, size, static_cast<const half*>(weight_host), row_id_host,
+                                   row_id_size, static_cast<const half*>(bias_host), nhead);
+    if (rc) { delete w; return rc; }
+    *out = new et_row_weight{w};
+    return ET_OK;
+}
+int et_row_weight_destroy(et_row_weight* w) {
+    if (w) { delete w->w; delete w; }
+    return ET_OK;
+}
+int et_row_linear(const et_row_weight* w, void* out, const void* in, int tokens, void* stream) {
+    ET_REQUIRE(w, "et_row_linear: null weight");
+    return et::tile_linear_run(w->w->tw, static_cast<half*>(out), static_cast<const half*>(in), tokens, 0,
+                               static_cast<cudaStream_t>(stream));
+}
+int et_row_weight_meta(const et_row_weight* w, int* nrow, int* row_id_size, const int** row_id_dev,
+                       const int** head_ptr_dev, int* head_ptr_host) {
+    ET_REQUIRE(w, "et_row_weight_meta: null weight");
+    if (nrow) *nrow = w->w->nrow;
+    if (row_id_size) *row_id_size = w->w->row_id_size;
+    if (row_id_dev) *row_id_dev = w->w->d_row_id;
+    if (head_ptr_dev) *head_ptr_dev = w->w->d_head_ptr;
+    if (head_ptr_host) std::copy(w->w->h_head_ptr.begin(), w->w->h_head_ptr.end(), head_ptr_host);
+    return ET_OK;
+}
+
+int et_attention_otf(void* out, const void* Q, const void* K, const void* V, const void* mask, int seq_len,
+                     int d_model, int nhead, void* stream) {
+    ET_REQUIRE(seq_len >= 0, "et_attention_otf: negative seq_len");
+    return et::attention_launch(static_cast<half*>(out), static_cast<const half*>(Q), static_cast<const half*>(K),
+                                static_cast<const half*>(V), nullptr, d_model, d_model, nullptr, nullptr, nullptr,
+                                static_cast<const half*>(mask), seq_len, nullptr, nullptr, 1, seq_len, seq_len,
+                                d_model, nhead, static_cast<cudaStream_t>(stream));
+}
+int et_attention_prune(void* out, const void* Q, const void* K, const void* V, const int* v_col_id,
+                       const int* v_head_ptr, int nnz_col_v, const void* mask, int seq_len, int d_model,
+                       int nhead, void* stream) {
+    ET_REQUIRE(seq_len >= 0 && nnz_col_v > 0, "et_attention_prune: bad dimensions");
+    ET_REQUIRE(v_col_id && v_head_ptr, "et_attention_prune: null index array");
+    return et::attention_launch(static_cast<half*>(out), static_cast<const half*>(Q), static_cast<const half*>(K),
+                                static_cast<const half*>(V), nullptr, d_model, nnz_col_v, nullptr, v_col_id,
+                                v_head_ptr, static_cast<const half*>(mask), seq_len, nullptr, nullptr, 1, seq_len,
+                                seq_len, d_model, nhead, static_cast<cudaStream_t>(stream));
+}
+int et_qk_scores(void* QK, const void* Q, const void* K, int seq_len, int d_model, int nhead, void* stream) {
+    return et::qk_scores_launch(static_cast<half*>(QK), static_cast<const half*>(Q), static_cast<const half*>(K), 1,
+                                seq_len, d_model, nhead, static_cast<cudaStream_t>(stream));
+}
+int et_attention_sharedqk(void* out, const void* QK, const void* V, const void* mask, int seq_len, int d_model,
+                          int nhead, void* stream) {
+    ET_REQUIRE(QK, "et_attention_sharedqk: null scores");
+    return et::attention_launch(static_cast<half*>(out), nullptr, nullptr, static_cast<const half*>(V),
+                                static_cast<const half*>(QK), d_model, d_model, nullptr, nullptr, nullptr,
+                                static_cast<const half*>(mask), seq_len, nullptr, nullptr, 1, seq_len, seq_len,
+                                d_model, nhead, static_cast<cudaStream_t>(stream));
+}
+int et_attention_batch(void* out, const void* Q, const void* K, const void* V, int qk_pitch, int v_pitch,
+                       const int* qk_head_ptr, const int* v_col_id, const int* v_head_ptr, const void* mask,
+                       int mask_ld, const int* cu_seqlens, const int* valid_lens, int batch, int uniform_len,
+                       int total_tokens, int d_model, int nhead, void* stream) {
+    return et::attention_launch(static_cast<half*>(out), static_cast<const half*>(Q), static_cast<const half*>(K),
+                                static_cast<const half*>(V), nullptr, qk_pitch, v_pitch, qk_head_ptr, v_col_id,
+                                v_head_ptr, static_cast<const half*>(mask), mask_ld, cu_seqlens, valid_lens, batch,
+                                uniform_len, total_tokens, d_model, nhead, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------------------ encoders
+static int take_tiles(Encoder* e, et_tile_weight** t, int first, int count, int d_model) {
+    for (int i = 0; i < count; ++i)
+        if (!t[i] || !t[i]->w) return et::fail(ET_ERR_INVALID, "encoder: null linear");
+    for (int i = 0; i < count; ++i) {
+        e->lin[first + i] = t[i]->w;   // ownership moves into the encoder, as the reference's rvalue ctor
+        t[i]->w = nullptr;
+    }
+    (void)d_model;
+    return ET_OK;
+}
+
+static int finish_create(et_encoder** out, std::unique_ptr<Encoder>& e) {
+    *out = new et_encoder{e.release()};
+    return ET_OK;
+}
+
+int et_encoder_tile_create(et_encoder** out, int kind, int d_model, int seq_len, int nheads, void* buffer,
+                           et_tile_weight* q, et_tile_weight* k, et_tile_weight* v, et_tile_weight* o,
+                           et_tile_weight* mlp1, et_tile_weight* mlp2, const void* ln_gamma_1,
+                           const void* ln_beta_1, const void* ln_gamma_2, const void* ln_beta_2,
+                           const void* mask_host) {
+    ET_REQUIRE(out, "et_encoder_tile_create: null output");
+    *out = nullptr;
+    ET_REQUIRE(kind == et::kTile || kind == et::kLength, "et_encoder_tile_create: kind must be 0 (tile) or 2 (length)");
+    auto e = std::make_unique<Encoder>();
+    e->kind = kind;
+    int rc = et::encoder_common(e.get(), d_model, seq_len, nheads, static_cast<half*>(buffer),
+                                static_cast<const half*>(ln_gamma_1), static_cast<const half*>(ln_beta_1),
+                                static_cast<const half*>(ln_gamma_2), static_cast<const half*>(ln_beta_2),
+                                static_cast<const half*>(mask_host));
+    if (rc) return rc;
+    et_tile_weight* t[6] = {q, k, v, o, mlp1, mlp2};
+    if ((rc = take_tiles(e.get(), t, 0, 6, d_model))) return rc;
+    return finish_create(out, e);
+}
+
+int et_encoder_prune_create(et_encoder** out, int d_model, int seq_len, int nheads, void* buffer,
+                            et_tile_weight* q, et_tile_weight* k, et_row_weight* v, et_tile_weight* o,
+                            et_tile_weight* mlp1, et_tile_weight* mlp2, const void* ln_gamma_1,
+                            const void* ln_beta_1, const void* ln_gamma_2, const void* ln_beta_2,
+                            const void* mask_host) {
+    ET_REQUIRE(out, "et_encoder_prune_create: null output");
+    *out = nullptr;
+    ET_REQUIRE(v && v->w, "et_encoder_prune_create: null V linear");
+    auto e = std::make_unique<Encoder>();
+    e->kind = et::kPrune;
+    int rc = et::encoder_common(e.get(), d_model, seq_len, nheads, static_cast<half*>(buffer),
+                                static_cast<const half*>(ln_gamma_1), static_cast<const half*>(ln_beta_1),
+                                static_cast<const half*>(ln_gamma_2), static_cast<const half*>(ln_beta_2),
+                                static_cast<const half*>(mask_host));
+    if (rc) return rc;
+    et_tile_weight* t01[2] = {q, k};
+    et_tile_weight* t35[3] = {o, mlp1, mlp2};
+    if ((rc = take_tiles(e.get(), t01, 0, 2, d_model))) return rc;
+    if ((rc = take_tiles(e.get(), t35, 3, 3, d_model))) return rc;
+    e->rv = v->w; v->w = nullptr;
+    return finish_create(out, e);
+}
+
+int et_encoder_prune_qkv_create(et_encoder** out, int d_model, int seq_len, int nheads, void* buffer,
+                                et_row_weight* q, et_row_weight* k, et_row_weight* v, et_tile_weight* o,
+                                et_tile_weight* mlp1, et_tile_weight* mlp2, const void* ln_gamma_1,
+                                const void* ln_beta_1, const void* ln_gamma_2, const void* ln_beta_2,
+                                const void* mask_host) {
+    ET_REQUIRE(out, "et_encoder_prune_qkv_create: null output");
+    *out = nullptr;
+    ET_REQUIRE(q && q->w && k && k->w && v && v->w, "et_encoder_prune_qkv_create: null linear");
+    ET_REQUIRE(q->w->row_id_size == k->w->row_id_size && q->w->h_head_ptr == k->w->h_head_ptr,
+               "et_encoder_prune_qkv_create: Q and K must retain the same dimensions per head");
+    auto e = std::make_unique<Encoder>();
+    e->kind = et::kPruneQKV;
+    int rc = et::encoder_common(e.get(), d_model, seq_len, nheads, static_cast<half*>(buffer),
+                                static_cast<const half*>(ln_gamma_1), static_cast<const half*>(ln_beta_1),
+                                static_cast<const half*>(ln_gamma_2), static_cast<const half*>(ln_beta_2),
+                                static_cast<const half*>(mask_host));
+    if (rc) return rc;
+    et_tile_weight* t35[3] = {o, mlp1, mlp2};
+    if ((rc = take_tiles(e.get(), t35, 3, 3, d_model))) return rc;
+    e->rq = q->w; q->w = nullptr;
+    e->rk = k->w; k->w = nullptr;
+    e->rv = v->w; v->w = nullptr;
+    return finish_create(out, e);
+}
+
+int et_encoder_destroy(et_encoder* enc) {
+    if (enc) { delete enc->e; delete enc; }
+    return ET_OK;
+}
+
+int et_encoder_set_materialize_scores(et_encoder* enc, int on) {
+    ET_REQUIRE(enc && enc->e, "et_encoder_set_materialize_scores: null encoder");
+    ET_REQUIRE(enc->e->kind == et::kLength, "et_encoder_set_materialize_scores: only the length encoder has that path");
+    enc->e->materialize_scores = on != 0;
+    return ET_OK;
+}
+
+size_t et_encoder_buffer_size(int kind, int d_model, int seq_len, int nheads) {
+    size_t n = (size_t)5 * d_model * seq_len;
+    if (kind == et::kLength) n += (size_t)nheads * seq_len * seq_len;
+    return n * sizeof(half);
+}
+
+size_t et_encoder_batch_buffer_size(int kind, int d_model, int total_tokens, int batch, int max_len, int nheads) {
+    size_t n = (size_t)5 * d_model * total_tokens;
+    if (kind == et::kLength) n += (size_t)batch * nheads * max_len * max_len;
+    return n * sizeof(half);
+}
+
+int et_encoder_run(et_encoder* enc, void* out, const void* in, void* stream) {
+    ET_REQUIRE(enc && enc->e && out && in, "et_encoder_run: null pointer");
+    Encoder* e = enc->e;
+    ET_REQUIRE(e->buffer, "et_encoder_run: the encoder was created without a scratch buffer");
+    return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in), e->buffer, e->seq_len,
+                               nullptr, nullptr, 1, e->seq_len, static_cast<cudaStream_t>(stream));
+}
+
+int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* seq_lens_host,
+                         const int* valid_lens_host, int batch, void* scratch, size_t scratch_bytes, void* stream) {
+    ET_REQUIRE(enc && enc->e && out && in && scratch, "et_encoder_run_batch: null pointer");
+    ET_REQUIRE(batch >= 0, "et_encoder_run_batch: negative batch");
+    Encoder* e = enc->e;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (batch == 0) return ET_OK;
+    ET_REQUIRE(seq_lens_host, "et_encoder_run_batch: null seq_lens");
+    std::vector<int> meta(2 * batch + 1);
+    meta[0] = 0;
+    bool uniform = true;
+    int max_len = 0;
+    for (int b = 0; b < batch; ++b) {
+        ET_REQUIRE(seq_lens_host[b] >= 0, "et_encoder_run_batch: negative sequence length");
+        ET_REQUIRE(!e->d_mask || seq_lens_host[b] <= e->seq_len, "et_encoder_run_batch: sequence longer than the mask");
+        meta[b + 1] = meta[b] + seq_lens_host[b];
+        meta[batch + 1 + b] = valid_lens_host ? valid_lens_host[b] : seq_lens_host[b];
+        uniform = uniform && seq_lens_host[b] == seq_lens_host[0];
+        max_len = std::max(max_len, seq_lens_host[b]);
+    }
+    const int T = meta[batch];
+    if (T == 0) return ET_OK;
+    const bool scores = e->kind == et::kLength && e->materialize_scores && uniform;
+    size_t need = (size_t)5 * e->d_model * T;
+    if (scores) need += (size_t)batch * e->nheads * max_len * max_len;
+    ET_REQUIRE(scratch_bytes >= need * sizeof(half), "et_encoder_run_batch: scratch buffer too small");
+    const int* cu = nullptr;
+    const int* vl = nullptr;
+    if (!uniform || valid_lens_host) {
+        if (e->lens_cap < 2 * batch + 1) {
+            cudaFree(e->d_lens);
+            e->d_lens = nullptr;
+            if (cudaMalloc(&e->d_lens, sizeof(int) * (2 * batch + 1)) != cudaSuccess)
+                return et::fail(ET_ERR_CUDA, "et_encoder_run_batch: cudaMalloc failed");
+            e->lens_cap = 2 * batch + 1;
+        }
+        int rc = et::cuda_status(cudaMemcpyAsync(e->d_lens, meta.data(), sizeof(int) * (2 * batch + 1),
+                                                 cudaMemcpyHostToDevice, st), "et_encoder_run_batch: lengths upload");
+        if (rc) return rc;
+        if (!uniform) cu = e->d_lens;
+        if (valid_lens_host) vl = e->d_lens + batch + 1;
+    }
+    return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in), static_cast<half*>(scratch),
+                               T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+}
+
+}  // extern "C"

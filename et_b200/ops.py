@@ -11,6 +11,9 @@ from . import check, lib, ptr, stream_ptr
 
 __all__ = [
     "skip_layernorm", "softmax_mask", "TileWeight", "tile_spmm_bias", "tile_spmm_cache_clear",
+    "RowWeight", "attention_otf", "attention_prune", "qk_scores", "attention_sharedqk", "attention_batch",
+    "gen_sparse_tile_mat", "gen_sparse_row_mat", "build_head_ptr", "Encoder", "encoder_buffer_size",
+    "encoder_batch_buffer_size", "KIND_TILE", "KIND_PRUNE", "KIND_LENGTH", "KIND_PRUNE_QKV",
 ]
 
 _i = ctypes.c_int
@@ -87,3 +90,176 @@ def tile_spmm_bias(Y, X, row_ptr, row_offset, data, bias, K=None, gelu=False, st
 
 def tile_spmm_cache_clear():
     check(lib().et_tile_spmm_cache_clear())
+
+
+# ---------------------------------------------------------------------------------- row-pruned linear
+class RowWeight:
+    """Row-pruned linear (the reference's Linear_row): only `row_id` output features are kept."""
+
+    def __init__(self, in_feat, out_feat, size, weight, row_id, bias, nhead):
+        weight = np.ascontiguousarray(weight, dtype=np.float16)
+        row_id = np.ascontiguousarray(row_id, dtype=np.int32)
+        bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float16)
+        self.in_feat, self.out_feat, self.size, self.nhead = in_feat, out_feat, size, nhead
+        self._h = ctypes.c_void_p(0)
+        check(lib().et_row_weight_create(ctypes.byref(self._h), _i(in_feat), _i(out_feat), _i(size),
+                                         ptr(weight), ptr(row_id), _i(len(row_id)), ptr(bias), _i(nhead)))
+        nrow, n = _i(0), _i(0)
+        rid, hp = ctypes.c_void_p(0), ctypes.c_void_p(0)
+        hph = (ctypes.c_int * (nhead + 1))()
+        check(lib().et_row_weight_meta(self._h, ctypes.byref(nrow), ctypes.byref(n), ctypes.byref(rid),
+                                       ctypes.byref(hp), hph))
+        self.nrow, self.row_id_size = nrow.value, n.value
+        self.row_id_dev, self.head_ptr_dev = rid, hp          # device addresses (c_void_p)
+        self.head_ptr = np.array(list(hph), dtype=np.int32)
+
+    def run(self, out, x, stream=None):
+        check(lib().et_row_linear(self._h, ptr(out), ptr(x), _i(x.shape[0]), stream_ptr(stream)))
+        return out
+
+    def close(self):
+        if self._h:
+            lib().et_row_weight_destroy(self._h)
+            self._h = ctypes.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---------------------------------------------------------------------------------- attention
+def attention_otf(out, Q, K, V, mask, seq_len, d_model, nhead, stream=None):
+    check(lib().et_attention_otf(ptr(out), ptr(Q), ptr(K), ptr(V), ptr(mask), _i(seq_len), _i(d_model),
+                                 _i(nhead), stream_ptr(stream)))
+    return out
+
+
+def attention_prune(out, Q, K, V, v_col_id, v_head_ptr, nnz_col_v, mask, seq_len, d_model, nhead, stream=None):
+    check(lib().et_attention_prune(ptr(out), ptr(Q), ptr(K), ptr(V), ptr(v_col_id), ptr(v_head_ptr),
+                                   _i(nnz_col_v), ptr(mask), _i(seq_len), _i(d_model), _i(nhead),
+                                   stream_ptr(stream)))
+    return out
+
+
+def qk_scores(QK, Q, K, seq_len, d_model, nhead, stream=None):
+    check(lib().et_qk_scores(ptr(QK), ptr(Q), ptr(K), _i(seq_len), _i(d_model), _i(nhead), stream_ptr(stream)))
+    return QK
+
+
+def attention_sharedqk(out, QK, V, mask, seq_len, d_model, nhead, stream=None):
+    check(lib().et_attention_sharedqk(ptr(out), ptr(QK), ptr(V), ptr(mask), _i(seq_len), _i(d_model),
+                                      _i(nhead), stream_ptr(stream)))
+    return out
+
+
+def attention_batch(out, Q, K, V, d_model, nhead, cu_seqlens=None, valid_lens=None, batch=1, uniform_len=0,
+                    total_tokens=None, mask=None, mask_ld=0, qk_pitch=None, v_pitch=None, qk_head_ptr=None,
+                    v_col_id=None, v_head_ptr=None, stream=None):
+    total = Q.shape[0] if total_tokens is None else total_tokens
+    check(lib().et_attention_batch(ptr(out), ptr(Q), ptr(K), ptr(V),
+                                   _i(Q.shape[1] if qk_pitch is None else qk_pitch),
+                                   _i(V.shape[1] if v_pitch is None else v_pitch), ptr(qk_head_ptr),
+                                   ptr(v_col_id), ptr(v_head_ptr), ptr(mask), _i(mask_ld), ptr(cu_seqlens),
+                                   ptr(valid_lens), _i(batch), _i(uniform_len), _i(total), _i(d_model),
+                                   _i(nhead), stream_ptr(stream)))
+    return out
+
+
+# ---------------------------------------------------------------------------------- format generators
+def gen_sparse_tile_mat(nrow, ncol, sparsity, seed, bernoulli=False):
+    cap = (nrow // 16) * (ncol // 16)
+    row_ptr = np.zeros(nrow // 16 + 1, dtype=np.int32)
+    row_offset = np.zeros(max(cap, 1), dtype=np.int32)
+    n = _i(0)
+    check(lib().et_gen_sparse_tile_mat(_i(nrow), _i(ncol), ctypes.c_float(sparsity), ctypes.c_uint64(seed),
+                                       _i(1 if bernoulli else 0), ptr(row_ptr), ptr(row_offset), _i(cap),
+                                       ctypes.byref(n)))
+    return row_ptr, row_offset[:n.value].copy()
+
+
+def gen_sparse_row_mat(nrow, sparsity, seed, nhead=0):
+    row_id = np.zeros(nrow, dtype=np.int32)
+    n = _i(0)
+    check(lib().et_gen_sparse_row_mat(_i(nrow), ctypes.c_float(sparsity), ctypes.c_uint64(seed), _i(nhead),
+                                      ptr(row_id), _i(nrow), ctypes.byref(n)))
+    return row_id[:n.value].copy()
+
+
+def build_head_ptr(row_id, nhead, out_feat):
+    row_id = np.ascontiguousarray(row_id, dtype=np.int32)
+    hp = np.zeros(nhead + 1, dtype=np.int32)
+    check(lib().et_build_head_ptr(ptr(row_id), _i(len(row_id)), _i(nhead), _i(out_feat), ptr(hp)))
+    return hp
+
+
+# ---------------------------------------------------------------------------------- encoder layers
+KIND_TILE, KIND_PRUNE, KIND_LENGTH, KIND_PRUNE_QKV = 0, 1, 2, 3
+
+
+def encoder_buffer_size(kind, d_model, seq_len, nheads):
+    f = lib().et_encoder_buffer_size
+    f.restype = ctypes.c_size_t
+    return int(f(_i(kind), _i(d_model), _i(seq_len), _i(nheads)))
+
+
+def encoder_batch_buffer_size(kind, d_model, total_tokens, batch, max_len, nheads):
+    f = lib().et_encoder_batch_buffer_size
+    f.restype = ctypes.c_size_t
+    return int(f(_i(kind), _i(d_model), _i(total_tokens), _i(batch), _i(max_len), _i(nheads)))
+
+
+class Encoder:
+    """One encoder layer (Encoder_tile / Encoder_prune / Encoder_length of the reference).
+
+    q, k, v, o, mlp1, mlp2 are TileWeight (or RowWeight where the kind prunes rows); the encoder takes
+    ownership of them. ln = (gamma1, beta1, gamma2, beta2) host arrays; mask host [seq_len, seq_len] or None;
+    buffer: device scratch tensor for run() (None if only run_batch is used)."""
+
+    def __init__(self, kind, d_model, seq_len, nheads, buffer, q, k, v, o, mlp1, mlp2, ln, mask=None):
+        self.kind, self.d_model, self.seq_len, self.nheads = kind, d_model, seq_len, nheads
+        self._buffer = buffer
+        self._lin = (q, k, v, o, mlp1, mlp2)
+        ln = [np.ascontiguousarray(a, dtype=np.float16) for a in ln]
+        mask = None if mask is None else np.ascontiguousarray(mask, dtype=np.float16)
+        self._h = ctypes.c_void_p(0)
+        L = lib()
+        common = (ptr(ln[0]), ptr(ln[1]), ptr(ln[2]), ptr(ln[3]), ptr(mask))
+        if kind in (KIND_TILE, KIND_LENGTH):
+            check(L.et_encoder_tile_create(ctypes.byref(self._h), _i(kind), _i(d_model), _i(seq_len), _i(nheads),
+                                           ptr(buffer), q._h, k._h, v._h, o._h, mlp1._h, mlp2._h, *common))
+        elif kind == KIND_PRUNE:
+            check(L.et_encoder_prune_create(ctypes.byref(self._h), _i(d_model), _i(seq_len), _i(nheads),
+                                            ptr(buffer), q._h, k._h, v._h, o._h, mlp1._h, mlp2._h, *common))
+        elif kind == KIND_PRUNE_QKV:
+            check(L.et_encoder_prune_qkv_create(ctypes.byref(self._h), _i(d_model), _i(seq_len), _i(nheads),
+                                                ptr(buffer), q._h, k._h, v._h, o._h, mlp1._h, mlp2._h, *common))
+        else:
+            raise ValueError("unknown encoder kind")
+
+    def run(self, out, x, stream=None):
+        check(lib().et_encoder_run(self._h, ptr(out), ptr(x), stream_ptr(stream)))
+        return out
+
+    def run_batch(self, out, x, seq_lens, scratch, valid_lens=None, stream=None):
+        seq_lens = np.ascontiguousarray(seq_lens, dtype=np.int32)
+        valid = None if valid_lens is None else np.ascontiguousarray(valid_lens, dtype=np.int32)
+        check(lib().et_encoder_run_batch(self._h, ptr(out), ptr(x), ptr(seq_lens), ptr(valid), _i(len(seq_lens)),
+                                         ptr(scratch), ctypes.c_size_t(scratch.numel() * scratch.element_size()),
+                                         stream_ptr(stream)))
+        return out
+
+    def set_materialize_scores(self, on):
+        check(lib().et_encoder_set_materialize_scores(self._h, _i(1 if on else 0)))
+
+    def close(self):
+        if self._h:
+            lib().et_encoder_destroy(self._h)
+            self._h = ctypes.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -70,6 +70,103 @@ int et_tile_spmm_bias(void* Y, const void* X, const int* W_row_ptr, const int* W
                       const void* W_data, int M, int N, int K, const void* bias, int gelu, void* stream);
 int et_tile_spmm_cache_clear(void);
 
+/* ---- row-pruned linear ---------------------------------------------------------------------
+ * Only row_id_size output features are kept; row_id_host[] holds their original indices, strictly
+ * ascending; weight_host is the compact [row_id_size x in_feat] matrix, bias_host[row_id_size] (NULL =
+ * zeros). The output has nrow = row_id_size rounded up to 16 columns (zero beyond row_id_size).
+ * head_ptr[h] = number of kept rows below h*(out_feat/nhead), h = 0..nhead.
+ * Replaces Linear_row::Linear_row (encoder/Linear.h:66-67, encoder/Linear.cu:60-91). */
+typedef struct et_row_weight et_row_weight;
+int et_row_weight_create(et_row_weight** out, int in_feat, int out_feat, int size, const void* weight_host,
+                         const int* row_id_host, int row_id_size, const void* bias_host, int nhead);
+int et_row_weight_destroy(et_row_weight* w);
+/* out[tokens x nrow] = in . W^T + bias. Replaces Linear_row::run (encoder/Linear.h:68-71) and
+ * row_spmm_add_bias_kernelLauncher (kernels/kernels.h:7-11, kernels/linear.cu:18-34); no cuBLAS handle. */
+int et_row_linear(const et_row_weight* w, void* out, const void* in, int tokens, void* stream);
+/* The public members of Linear_row that the encoder reads (encoder/encoder.cu:76-79): any of the
+ * output pointers may be NULL. head_ptr_host receives nhead+1 ints. */
+int et_row_weight_meta(const et_row_weight* w, int* nrow, int* row_id_size, const int** row_id_dev,
+                       const int** head_ptr_dev, int* head_ptr_host);
+
+/* ---- attention --------------------------------------------------------------------------------
+ * out[seq_len x d_model], head h in columns [h*hd, (h+1)*hd): softmax(Q_h K_h^T / sqrt(hd) + mask) V_h.
+ * mask: additive [seq_len x seq_len] fp16 shared by all heads, or NULL. Any seq_len >= 0.
+ * Replaces OTF_attention_kernelLauncher (kernels/kernels.h:22-24, kernels/attention.cu:122-134). */
+int et_attention_otf(void* out, const void* Q, const void* K, const void* V, const void* mask, int seq_len,
+                     int d_model, int nhead, void* stream);
+/* V compact [seq_len x nnz_col_v]; head h owns compact columns [v_head_ptr[h], v_head_ptr[h+1]); result
+ * column j is stored at out column v_col_id[j], every other out column is written as 0.
+ * Replaces Prune_attention_kernelLauncher (kernels/kernels.h:26-30, kernels/attention.cu:252-271). */
+int et_attention_prune(void* out, const void* Q, const void* K, const void* V, const int* v_col_id,
+                       const int* v_head_ptr, int nnz_col_v, const void* mask, int seq_len, int d_model,
+                       int nhead, void* stream);
+/* QK[nhead][seq_len][seq_len] = Q_h K_h^T / sqrt(hd), Q and K with row pitch d_model.
+ * Replaces the cublasHgemmStridedBatched call of Encoder_length::run (encoder/encoder.cu:126-130). */
+int et_qk_scores(void* QK, const void* Q, const void* K, int seq_len, int d_model, int nhead, void* stream);
+/* out = softmax(QK + mask) V per head from precomputed scores.
+ * Replaces sharedQK_attention_kernelLauncher (kernels/kernels.h:32-34, kernels/attention.cu:342-350). */
+int et_attention_sharedqk(void* out, const void* QK, const void* V, const void* mask, int seq_len,
+                          int d_model, int nhead, void* stream);
+/* Batched, variable-length form (no counterpart in the reference, which handles one sequence per call):
+ * sequences are packed back to back; cu_seqlens (device, batch+1 ints) gives their token offsets, or NULL
+ * for `batch` sequences of uniform_len tokens. valid_lens (device, may be NULL) excludes keys at or beyond
+ * valid_lens[b] (key padding). Q and K share qk_pitch; qk_head_ptr / v_head_ptr + v_col_id (device, may be
+ * NULL) select compact per-head column windows as in et_attention_prune. */
+int et_attention_batch(void* out, const void* Q, const void* K, const void* V, int qk_pitch, int v_pitch,
+                       const int* qk_head_ptr, const int* v_col_id, const int* v_head_ptr, const void* mask,
+                       int mask_ld, const int* cu_seqlens, const int* valid_lens, int batch, int uniform_len,
+                       int total_tokens, int d_model, int nhead, void* stream);
+
+/* ---- pruned-format generators (host) ----------------------------------------------------------
+ * Seeded and reproducible. bernoulli == 0 keeps exactly floor(total*(1-sparsity)) tiles (a block-row's
+ * tiles in draw order); otherwise each tile is kept with probability 1-sparsity (ascending offsets).
+ * Replaces gen_sparse_tile_mat (test/tile_mat.cu:5-34) and gen_sparse_row_mat (test/row_mat.cu:5-14). */
+int et_gen_sparse_tile_mat(int nrow, int ncol, float sparsity, uint64_t seed, int bernoulli, int* row_ptr,
+                           int* row_offset, int cap, int* ntile);
+int et_gen_sparse_row_mat(int nrow, float sparsity, uint64_t seed, int nhead, int* row_id, int cap, int* nkeep);
+int et_build_head_ptr(const int* row_id, int n, int nhead, int out_feat, int* head_ptr);
+
+/* ---- encoder layers ----------------------------------------------------------------------------
+ * One post-LN encoder layer: Q,K,V linears -> attention -> output linear -> add+LayerNorm -> MLP1 (GELU)
+ * -> MLP2 -> add+LayerNorm (encoder/encoder.cu:20-45). LayerNorm vectors (d_model) and mask
+ * (seq_len x seq_len additive, may be NULL) are HOST pointers and are copied; `buffer` is a DEVICE
+ * scratch of et_encoder_buffer_size bytes owned by the caller (may be NULL if only run_batch is used).
+ * The encoder takes ownership of the linears passed in (their handles stay valid only for destroy),
+ * as the reference's constructors take them by rvalue. kind: 0 = Encoder_tile, 2 = Encoder_length
+ * (encoder/encoder.h:56-77, :102-134). */
+typedef struct et_encoder et_encoder;
+int et_encoder_tile_create(et_encoder** out, int kind, int d_model, int seq_len, int nheads, void* buffer,
+                           et_tile_weight* q, et_tile_weight* k, et_tile_weight* v, et_tile_weight* o,
+                           et_tile_weight* mlp1, et_tile_weight* mlp2, const void* ln_gamma_1,
+                           const void* ln_beta_1, const void* ln_gamma_2, const void* ln_beta_2,
+                           const void* mask_host);
+/* Encoder_prune (encoder/encoder.h:79-100): V is row-pruned. */
+int et_encoder_prune_create(et_encoder** out, int d_model, int seq_len, int nheads, void* buffer,
+                            et_tile_weight* q, et_tile_weight* k, et_row_weight* v, et_tile_weight* o,
+                            et_tile_weight* mlp1, et_tile_weight* mlp2, const void* ln_gamma_1,
+                            const void* ln_beta_1, const void* ln_gamma_2, const void* ln_beta_2,
+                            const void* mask_host);
+/* Extension: Q, K and V all row-pruned; Q and K must keep the same rows per head. */
+int et_encoder_prune_qkv_create(et_encoder** out, int d_model, int seq_len, int nheads, void* buffer,
+                                et_row_weight* q, et_row_weight* k, et_row_weight* v, et_tile_weight* o,
+                                et_tile_weight* mlp1, et_tile_weight* mlp2, const void* ln_gamma_1,
+                                const void* ln_beta_1, const void* ln_gamma_2, const void* ln_beta_2,
+                                const void* mask_host);
+int et_encoder_destroy(et_encoder* enc);
+/* Encoder_base::buffer_size / Encoder_length::buffer_size (encoder/encoder.h:51-53, :129-133), in bytes. */
+size_t et_encoder_buffer_size(int kind, int d_model, int seq_len, int nheads);
+size_t et_encoder_batch_buffer_size(int kind, int d_model, int total_tokens, int batch, int max_len, int nheads);
+/* Encoder_*::run(out, in) (encoder/encoder.h:76): one sequence of seq_len tokens; out may alias in. */
+int et_encoder_run(et_encoder* enc, void* out, const void* in, void* stream);
+/* Extension: a batch of packed sequences, seq_lens_host[batch] tokens each (any length >= 0, at most
+ * seq_len when the encoder has a mask); valid_lens_host (may be NULL) marks keys at or beyond it as padding.
+ * scratch: device buffer of et_encoder_batch_buffer_size bytes. */
+int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* seq_lens_host,
+                         const int* valid_lens_host, int batch, void* scratch, size_t scratch_bytes, void* stream);
+/* Length encoder only: route attention through scores materialised in HBM (the reference's structure,
+ * encoder/encoder.cu:126-136) instead of the default on-the-fly kernel. Equal-length batches only. */
+int et_encoder_set_materialize_scores(et_encoder* enc, int on);
+
 #ifdef __cplusplus
 }
 #endif
