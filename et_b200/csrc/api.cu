@@ -56,3 +56,9 @@ extern "C" int et_tile_spmm_cache_clear(void) {
     et::tile_spmm_cache_clear();
     return ET_OK;
 }
+
+// Not part of the public header: used by profiling builds of the library only.
+extern "C" int et_debug_set_gemm_profile_buffer(void* dev_buf) {
+    et::tile_gemm_set_profile_buffer(static_cast<long long*>(dev_buf));
+    return ET_OK;
+}

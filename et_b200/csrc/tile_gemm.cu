@@ -44,7 +44,8 @@ constexpr int kThreads = 32 * (2 + kIssuers);
 constexpr int kXStageBytes = kSlab * kKC * 2;  // 16 KB
 constexpr int kHeaderBytes = 64;
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 220 * 1024;
+constexpr int kSmemBudget = 218 * 1024;
+constexpr int kMaxKChunks = 512;    // in_feat up to 32768
 
 struct GemmParams {
     const uint2* dir;        // per (chunk, k-chunk): {offset, size} in 16-byte units
@@ -53,7 +54,14 @@ struct GemmParams {
     const half* bias;
     int T, N, k_chunks, nb, stage_b_bytes, num_stages, gelu;
     int* err;
+    long long* prof;         // optional per-role clock64 stamps of CTA (0,0) (ET_GEMM_PROFILE builds only)
 };
+
+#ifdef ET_GEMM_PROFILE
+#define ET_STAMP(slot) do { if (p.prof && blockIdx.x == 0 && blockIdx.y == 0) p.prof[(slot)] = clock64(); } while (0)
+#else
+#define ET_STAMP(slot) do { } while (0)
+#endif
 
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
@@ -88,6 +96,7 @@ struct Shared {
     uint64_t acc_done;                // 8 issuer commits after the last chunk
     uint32_t tmem_base;
     volatile int abort;
+    uint2 dir[kMaxKChunks];           // this CTA's row of the block directory
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -99,6 +108,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int slab = blockIdx.x, chunk = blockIdx.y;
     const int S = p.num_stages;
+    if (tid == 0) ET_STAMP(0);
 
     if (tid == 0) {
         for (int s = 0; s < S; ++s) {
@@ -117,11 +127,15 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
     if (warp == 1) {
         tmem_alloc(&sh->tmem_base, 512);
         tmem_relinquish();
+    } else if (warp == 0) {
+        const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
+        for (int i = lane; i < p.k_chunks; i += 32) sh->dir[i] = __ldg(gdir + i);
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
+    if (tid == 0) ET_STAMP(1);
 
     // Accumulators start at zero: block-rows without tiles are legal and every UMMA accumulates.
     if (warp >= 2) {
@@ -134,19 +148,20 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
     __syncthreads();
     tc_fence_after();
 
-    const uint2* dir = p.dir + (size_t)chunk * p.k_chunks;
+    if (tid == 0) ET_STAMP(2);
 
     if (warp == 0) {
         // ---------------- producer: TMA activations + bulk copy of the weight block
         if (lane == 0) {
-            uint2 d = dir[0];
             int issued = 0;
             for (int kc = 0; kc < p.k_chunks; ++kc) {
                 const int s = kc % S;
                 const uint32_t ph = (uint32_t)(kc / S) & 1u;
-                uint2 dn = (kc + 1 < p.k_chunks) ? dir[kc + 1] : make_uint2(0, 0);
+                const uint2 d = sh->dir[kc];
                 if (sh->abort) break;
-                if (!mbar_wait(&sh->stage_free[s], ph ^ 1u)) {
+                const bool free_ok = mbar_wait(&sh->stage_free[s], ph ^ 1u);
+                ET_STAMP(900 + kc);
+                if (!free_ok) {
                     atomicExch(p.err, 11);
                     sh->abort = 1;
                     break;
@@ -154,9 +169,11 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
                 uint8_t* st = smem + (size_t)s * stage_bytes;
                 const uint32_t bbytes = d.y * 16u;
                 mbar_expect_tx(&sh->full[s], kXStageBytes + bbytes);
+                ET_STAMP(1000 + kc);
                 tma_load_2d(st, &tmX, kc * kKC, slab * kSlab, &sh->full[s]);
+                ET_STAMP(1100 + kc);
                 bulk_load(st + kXStageBytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[s]);
-                d = dn;
+                ET_STAMP(100 + kc);
                 ++issued;
             }
             // Leaving early: wait (bounded) for the copies still in flight before the CTA exits.
@@ -170,13 +187,17 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
             for (int kc = 0; kc < p.k_chunks; ++kc) {
                 const int s = kc % S, j = kc % kABufs;
                 if (sh->abort) break;
-                if (!mbar_wait(&sh->full[s], (uint32_t)(kc / S) & 1u) ||
-                    !mbar_wait(&sh->a_free[j], ((uint32_t)(kc / kABufs) & 1u) ^ 1u)) {
+                bool got = mbar_wait(&sh->full[s], (uint32_t)(kc / S) & 1u);
+                ET_STAMP(700 + kc);
+                got = got && mbar_wait(&sh->a_free[j], ((uint32_t)(kc / kABufs) & 1u) ^ 1u);
+                ET_STAMP(800 + kc);
+                if (!got) {
                     atomicExch(p.err, 12);
                     sh->abort = 1;
                     break;
                 }
                 tc_fence_after();
+                ET_STAMP(200 + kc);
                 const uint32_t xa = smem_u32(smem + (size_t)s * stage_bytes);
 #pragma unroll
                 for (int sl = 0; sl < kSlices; ++sl)
@@ -184,6 +205,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
                                    make_smem_desc(xa + sl * 32, 16, 1024, 2));
                 umma_commit(&sh->a_ready[j]);
                 umma_commit(&sh->stage_free[s]);
+                ET_STAMP(300 + kc);
             }
         }
     } else {
@@ -195,8 +217,17 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
         for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
             const int s = kc % S, j = kc % kABufs;
             if (sh->abort) { ok = false; break; }
-            if (!mbar_wait(&sh->full[s], (uint32_t)(kc / S) & 1u) ||
-                !mbar_wait(&sh->a_ready[j], (uint32_t)(kc / kABufs) & 1u)) {
+            // one lane polls; 256 threads spinning on the same mbarrier words slow every other
+            // barrier operation of the CTA (TMA completion included)
+            int got = 1;
+            if (lane == 0) {
+                got = mbar_wait(&sh->full[s], (uint32_t)(kc / S) & 1u);
+                if (w == 0) ET_STAMP(400 + kc);
+                got = got && mbar_wait(&sh->a_ready[j], (uint32_t)(kc / kABufs) & 1u);
+                if (w == 0) ET_STAMP(500 + kc);
+            }
+            got = __shfl_sync(0xffffffffu, got, 0);
+            if (!got) {
                 if (lane == 0) atomicExch(p.err, 13);
                 sh->abort = 1;
                 ok = false;
@@ -221,17 +252,24 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
                 umma_commit(&sh->stage_free[s]);
                 umma_commit(&sh->a_free[j]);
             }
+            if (w == 0 && lane == 0) ET_STAMP(600 + kc);
             __syncwarp();
         }
         if (elect_one()) umma_commit(&sh->acc_done);
         __syncwarp();
 
         // ---------------- epilogue: TMEM -> registers -> bias / GELU -> fp16 -> global
-        if (ok && !mbar_wait(&sh->acc_done, 0)) {
-            if (lane == 0) atomicExch(p.err, 14);
-            ok = false;
+        if (ok) {
+            int done = 1;
+            if (lane == 0) done = mbar_wait(&sh->acc_done, 0);
+            done = __shfl_sync(0xffffffffu, done, 0);
+            if (!done) {
+                if (lane == 0) atomicExch(p.err, 14);
+                ok = false;
+            }
         }
         tc_fence_after();
+        if (w == 0 && lane == 0) ET_STAMP(3);
         if (ok) {
             const int q = warp & 3;
             const int row = slab * kSlab + q * 32 + lane;
@@ -269,6 +307,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    if (tid == 0) ET_STAMP(4);
     if (warp == 1) tmem_dealloc(tmem, 512);
 }
 
@@ -314,6 +353,7 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     w->nb = nb_override > 0 ? std::min(nb_override, kMaxNB) : choose_nb(NBR, size_hint);
     w->n_chunks = (NBR + w->nb - 1) / w->nb;
     w->k_chunks = (K + kKC - 1) / kKC;
+    if (w->k_chunks > kMaxKChunks) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: in_feat above 32768"); }
 
     // Bucket tiles by (chunk, k-chunk, issuing warp).
     struct Ent { int tile; int slice; int lb; };
@@ -393,6 +433,9 @@ int tile_weight_set_bias_device(TileWeight* w, const half* bias_dev, cudaStream_
     return cuda_status(cudaMemcpyAsync(w->d_bias, bias_dev, (size_t)w->N * sizeof(half), cudaMemcpyDeviceToDevice, st), "bias copy");
 }
 
+static long long* g_prof = nullptr;
+void tile_gemm_set_profile_buffer(long long* dev_buf) { g_prof = dev_buf; }
+
 int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st) {
     if (!w || !Y || !X) return fail(ET_ERR_INVALID, "tile linear: null pointer");
     if (T < 0) return fail(ET_ERR_INVALID, "tile linear: negative token count");
@@ -411,6 +454,7 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     p.dir = w->d_dir; p.stream = w->d_stream; p.Y = Y; p.bias = w->d_bias;
     p.T = T; p.N = w->N; p.k_chunks = w->k_chunks; p.nb = w->nb;
     p.stage_b_bytes = w->stage_b_bytes; p.num_stages = w->num_stages; p.gelu = gelu; p.err = w->d_err;
+    p.prof = g_prof;
     const size_t smem = (size_t)w->num_stages * (kXStageBytes + w->stage_b_bytes) + sizeof(Shared) + 1024;
     dim3 grid((T + kSlab - 1) / kSlab, w->n_chunks);
     tile_gemm_kernel<<<grid, kThreads, smem, st>>>(tm, p);

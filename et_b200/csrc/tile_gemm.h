@@ -20,5 +20,7 @@ void tile_weight_info(const TileWeight* w, int* info6);
 int tile_spmm_raw(half* Y, const half* X, const int* row_ptr, const int* row_offset, const half* data,
                   int M, int N, int K, const half* bias, int gelu, cudaStream_t st);
 void tile_spmm_cache_clear();
+// Profiling builds (-DET_GEMM_PROFILE): device buffer of >= 1024 clock64 stamps written by CTA (0,0).
+void tile_gemm_set_profile_buffer(long long* dev_buf);
 
 }  // namespace et
