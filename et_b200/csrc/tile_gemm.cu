@@ -44,7 +44,7 @@ constexpr int kThreads = 32 * (2 + kIssuers);
 constexpr int kXStageBytes = kSlab * kKC * 2;  // 16 KB
 constexpr int kHeaderBytes = 64;
 constexpr int kMaxStages = 8;
-constexpr int kSmemBudget = 218 * 1024;
+constexpr int kSmemMax = 232448;    // 227 KB: the per-CTA opt-in limit of sm_100
 constexpr int kMaxKChunks = 512;    // in_feat up to 32768
 
 struct GemmParams {
@@ -402,7 +402,7 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     }
     w->stage_b_bytes = (int)((max_block + 1023) / 1024 * 1024);
     const int stage = kXStageBytes + w->stage_b_bytes;
-    w->num_stages = std::min(kMaxStages, (kSmemBudget - 1024) / stage);
+    w->num_stages = std::min(kMaxStages, (kSmemMax - 1024 - (int)sizeof(Shared)) / stage);
     if (w->num_stages < 2) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
     w->num_stages = std::min(w->num_stages, std::max(2, w->k_chunks));
     w->stream_bytes = stream.size();
@@ -447,7 +447,7 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(tile_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget + 2048);
+        attr_err = cudaFuncSetAttribute(tile_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
     });
     if (attr_err != cudaSuccess) return cuda_status(attr_err, "tile linear: shared memory opt-in");
     GemmParams p;
