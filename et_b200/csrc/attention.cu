@@ -17,6 +17,7 @@
 //
 // Tensor path: warp-level mma.sync m16n8k16 with ldmatrix-fed fragments (flash-style online softmax,
 // P stays in registers). Widths per head up to 64 are supported (zero-padded in shared memory).
+#include <mutex>
 #include "common.h"
 
 namespace et {
@@ -364,6 +365,62 @@ int attention_launch(half* Z, const half* Q, const half* K, const half* V, const
                                 : batch * ((uniform_len + kBQ - 1) / kBQ);
     attention_kernel<<<dim3(nblk, nhead), 128, 0, st>>>(p);
     return cuda_status(cudaGetLastError(), "attention launch");
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// Attention through materialised scores for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they run a layer: code that
+// runs inside a real-time serving loop with a fixed memory plan, a plugin loaded into a process whose
+// allocator owns the whole device, or a caller that is between cudaStreamBeginCapture and
+// cudaStreamEndCapture for unrelated work on another stream. For them the score matrices
+// [nhead][seq_len][seq_len] live in the array below, which is part of the library image: every GPU that
+// loads the library holds these 8 MiB until the process exits.
+//
+// The array is shared by all calls on a device and keeps the contents of the previous call. Nothing
+// has to be cleared: the score kernel writes every element that the attention kernel later reads.
+// Two calls that overlap on the GPU (different streams, or different host threads) race on it;
+// serialise them on one stream.
+constexpr size_t kStaticScoreHalfs = (size_t)16 * 512 * 512;   // e.g. 16 heads x 512 x 512
+static __device__ __align__(256) half g_static_scores[kStaticScoreHalfs];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+half* g_static_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+// In host code `g_static_scores` is only a handle for the runtime, not a device address; the address a
+// kernel can use is obtained once per device, with that device current.
+static int static_scores_address(half** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e, "static scores: cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(ET_ERR_UNSUPPORTED, "static scores: device ordinal above 63");
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scores);
+        if (e != cudaSuccess) return cuda_status(e, "static scores: cudaGetSymbolAddress");
+        g_static_ptr[dev] = static_cast<half*>(p);
+    }
+    *out = g_static_ptr[dev];
+    return ET_OK;
+}
+
+int attention_static_scores(half* Z, const half* Q, const half* K, const half* V, const half* mask, int seq_len,
+                            int d_model, int nhead, cudaStream_t st) {
+    if (seq_len < 0 || nhead <= 0 || d_model <= 0) return fail(ET_ERR_INVALID, "static-score attention: bad dimensions");
+    if ((size_t)nhead * seq_len * seq_len > kStaticScoreHalfs)
+        return fail(ET_ERR_UNSUPPORTED,
+                    "static-score attention: nhead*seq_len*seq_len exceeds the built-in score buffer (16*512*512 elements)");
+    half* scores = nullptr;
+    int rc = static_scores_address(&scores);
+    if (rc) return rc;
+    if ((rc = qk_scores_launch(scores, Q, K, 1, seq_len, d_model, nhead, st))) return rc;
+    return attention_launch(Z, nullptr, nullptr, V, scores, d_model, d_model, nullptr, nullptr, nullptr, mask, seq_len,
+                            nullptr, nullptr, 1, seq_len, seq_len, d_model, nhead, st);
 }
 
 }  // namespace et

@@ -16,4 +16,9 @@ int attention_launch(half* Z, const half* Q, const half* K, const half* V, const
 int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, int d_model, int nhead,
                      cudaStream_t st);
 
+// Same result as the on-the-fly form for one sequence, through scores held in a device array that is part
+// of the library image (no allocation). seq_len*seq_len*nhead is limited to 16*512*512.
+int attention_static_scores(half* Z, const half* Q, const half* K, const half* V, const half* mask, int seq_len,
+                            int d_model, int nhead, cudaStream_t st);
+
 }  // namespace et

@@ -242,6 +242,14 @@ int et_attention_sharedqk(void* out, const void* QK, const void* V, const void* 
                                 static_cast<const half*>(mask), seq_len, nullptr, nullptr, 1, seq_len, seq_len,
                                 d_model, nhead, static_cast<cudaStream_t>(stream));
 }
+int et_attention_static_scores(void* out, const void* Q, const void* K, const void* V, const void* mask,
+                               int seq_len, int d_model, int nhead, void* stream) {
+    ET_REQUIRE(out && Q && K && V, "et_attention_static_scores: null pointer");
+    return et::attention_static_scores(static_cast<half*>(out), static_cast<const half*>(Q),
+                                       static_cast<const half*>(K), static_cast<const half*>(V),
+                                       static_cast<const half*>(mask), seq_len, d_model, nhead,
+                                       static_cast<cudaStream_t>(stream));
+}
 int et_attention_batch(void* out, const void* Q, const void* K, const void* V, int qk_pitch, int v_pitch,
                        const int* qk_head_ptr, const int* v_col_id, const int* v_head_ptr, const void* mask,
                        int mask_ld, const int* cu_seqlens, const int* valid_lens, int batch, int uniform_len,

@@ -11,7 +11,7 @@ from . import check, lib, ptr, stream_ptr
 
 __all__ = [
     "skip_layernorm", "softmax_mask", "TileWeight", "tile_spmm_bias", "tile_spmm_cache_clear",
-    "RowWeight", "attention_otf", "attention_prune", "qk_scores", "attention_sharedqk", "attention_batch",
+    "RowWeight", "attention_otf", "attention_prune", "qk_scores", "attention_sharedqk", "attention_batch", "attention_static_scores",
     "gen_sparse_tile_mat", "gen_sparse_row_mat", "build_head_ptr", "Encoder", "encoder_buffer_size",
     "encoder_batch_buffer_size", "KIND_TILE", "KIND_PRUNE", "KIND_LENGTH", "KIND_PRUNE_QKV",
 ]
@@ -151,6 +151,13 @@ def qk_scores(QK, Q, K, seq_len, d_model, nhead, stream=None):
 def attention_sharedqk(out, QK, V, mask, seq_len, d_model, nhead, stream=None):
     check(lib().et_attention_sharedqk(ptr(out), ptr(QK), ptr(V), ptr(mask), _i(seq_len), _i(d_model),
                                       _i(nhead), stream_ptr(stream)))
+    return out
+
+
+def attention_static_scores(out, Q, K, V, mask, seq_len, d_model, nhead, stream=None):
+    """et_attention_otf's result through the library's built-in score buffer: allocates nothing."""
+    check(lib().et_attention_static_scores(ptr(out), ptr(Q), ptr(K), ptr(V), ptr(mask), _i(seq_len), _i(d_model),
+                                           _i(nhead), stream_ptr(stream)))
     return out
 
 

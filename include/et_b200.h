@@ -107,6 +107,16 @@ int et_qk_scores(void* QK, const void* Q, const void* K, int seq_len, int d_mode
  * Replaces sharedQK_attention_kernelLauncher (kernels/kernels.h:32-34, kernels/attention.cu:342-350). */
 int et_attention_sharedqk(void* out, const void* QK, const void* V, const void* mask, int seq_len,
                           int d_model, int nhead, void* stream);
+/* Attention for callers that cannot allocate device memory (no counterpart in the reference). Same
+ * arguments and result as et_attention_otf, computed through score matrices kept in an 8 MiB device array
+ * that is part of the library image, so the call allocates nothing: not with cudaMalloc and not through
+ * any library. Meant for hosts with a fixed memory plan (a real-time loop, a plugin whose host process
+ * owns the allocator). Limit: nhead * seq_len * seq_len <= 16 * 512 * 512, otherwise ET_ERR_UNSUPPORTED.
+ * The first call on each device looks up the array's device address; make that call before any stream
+ * capture starts. All calls on a device share the array: issue them on one stream, calls that overlap
+ * on the GPU race. Nothing needs clearing between calls. */
+int et_attention_static_scores(void* out, const void* Q, const void* K, const void* V, const void* mask,
+                               int seq_len, int d_model, int nhead, void* stream);
 /* Batched, variable-length form (no counterpart in the reference, which handles one sequence per call):
  * sequences are packed back to back; cu_seqlens (device, batch+1 ints) gives their token offsets, or NULL
  * for `batch` sequences of uniform_len tokens. valid_lens (device, may be NULL) excludes keys at or beyond
