@@ -52,8 +52,10 @@ extern "C" int et_tile_spmm_bias(void* Y, const void* X, const int* W_row_ptr,
                              W_row_offset, static_cast<const half*>(W_data), M, N, K,
                              static_cast<const half*>(bias), gelu, static_cast<cudaStream_t>(stream));
 }
+namespace et { void row_spmm_cache_clear(); }
 extern "C" int et_tile_spmm_cache_clear(void) {
     et::tile_spmm_cache_clear();
+    et::row_spmm_cache_clear();
     return ET_OK;
 }
 

@@ -6,7 +6,10 @@
 // a batch of packed variable-length sequences is a first-class input (run_batch); every failure is a
 // status code instead of exit(1).
 #include <algorithm>
+#include <map>
 #include <memory>
+#include <mutex>
+#include <tuple>
 #include <vector>
 #include "attention.h"
 #include "common.h"
@@ -85,6 +88,42 @@ static int row_weight_create(RowWeight** out, int in_feat, int out_feat, int siz
     cudaMemcpy(w->d_head_ptr, w->h_head_ptr.data(), sizeof(int) * (nhead + 1), cudaMemcpyHostToDevice);
     *out = w.release();
     return ET_OK;
+}
+
+namespace {
+std::mutex g_row_mu;
+std::map<std::tuple<const void*, int, int>, TileWeight*> g_row_cache;
+}  // namespace
+
+int row_spmm_raw(half* out, const half* in, const half* weight, const half* bias, int M, int N, int K, cudaStream_t st) {
+    TileWeight* tw = nullptr;
+    {
+        std::lock_guard<std::mutex> lk(g_row_mu);
+        auto key = std::make_tuple((const void*)weight, N, K);
+        auto it = g_row_cache.find(key);
+        if (it == g_row_cache.end()) {
+            std::vector<half> hw((size_t)N * K);
+            if (cudaMemcpy(hw.data(), weight, hw.size() * sizeof(half), cudaMemcpyDeviceToHost) != cudaSuccess)
+                return fail(ET_ERR_CUDA, "row spmm: cannot read the weight");
+            std::vector<half> data;
+            std::vector<int> rp, ro;
+            dense_to_tiles(hw.data(), N, K, data, rp, ro);
+            int rc = tile_weight_pack(&tw, K, N, M, (long)ro.size(), data.data(), rp.data(), ro.data(), nullptr, 0);
+            if (rc) return rc;
+            g_row_cache[key] = tw;
+        } else {
+            tw = it->second;
+        }
+    }
+    int rc = tile_weight_set_bias_device(tw, bias, st);
+    if (rc) return rc;
+    return tile_linear_run(tw, out, in, M, 0, st);
+}
+
+void row_spmm_cache_clear() {
+    std::lock_guard<std::mutex> lk(g_row_mu);
+    for (auto& kv : g_row_cache) tile_weight_free(kv.second);
+    g_row_cache.clear();
 }
 
 // ------------------------------------------------------------------------------ encoder layer
@@ -200,6 +239,16 @@ int et_row_linear(const et_row_weight* w, void* out, const void* in, int tokens,
     ET_REQUIRE(w, "et_row_linear: null weight");
     return et::tile_linear_run(w->w->tw, static_cast<half*>(out), static_cast<const half*>(in), tokens, 0,
                                static_cast<cudaStream_t>(stream));
+}
+// Launcher-level form with a DEVICE-resident dense compact weight [N x K] (N a multiple of 16 as the
+// reference pads it). The packed form is built on first use (device-to-host copy, synchronous) and cached
+// by weight address; et_tile_spmm_cache_clear() drops these entries too.
+int et_row_spmm_bias(void* out, const void* in, const void* weight, const void* bias, int M, int N, int K,
+                     void* stream) {
+    ET_REQUIRE(out && in && weight && bias, "et_row_spmm_bias: null pointer");
+    ET_REQUIRE(N > 0 && K > 0 && N % 16 == 0 && K % 16 == 0, "et_row_spmm_bias: N and K must be positive multiples of 16");
+    return et::row_spmm_raw(static_cast<half*>(out), static_cast<const half*>(in), static_cast<const half*>(weight),
+                            static_cast<const half*>(bias), M, N, K, static_cast<cudaStream_t>(stream));
 }
 int et_row_weight_meta(const et_row_weight* w, int* nrow, int* row_id_size, const int** row_id_dev,
                        const int** head_ptr_dev, int* head_ptr_host) {

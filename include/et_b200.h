@@ -83,6 +83,12 @@ int et_row_weight_destroy(et_row_weight* w);
 /* out[tokens x nrow] = in . W^T + bias. Replaces Linear_row::run (encoder/Linear.h:68-71) and
  * row_spmm_add_bias_kernelLauncher (kernels/kernels.h:7-11, kernels/linear.cu:18-34); no cuBLAS handle. */
 int et_row_linear(const et_row_weight* w, void* out, const void* in, int tokens, void* stream);
+/* Same contraction from a DEVICE-resident dense compact weight [N x K], N and K multiples of 16 (the
+ * reference pads N to 16): out[M x N] = in[M x K] . weight^T + bias. Packed on first use and cached by
+ * weight address (et_tile_spmm_cache_clear drops the cache). Replaces row_spmm_add_bias_kernelLauncher
+ * (kernels/kernels.h:7-11, kernels/linear.cu:18-34) without its cuBLAS handle and algorithm. */
+int et_row_spmm_bias(void* out, const void* in, const void* weight, const void* bias, int M, int N, int K,
+                     void* stream);
 /* The public members of Linear_row that the encoder reads (encoder/encoder.cu:76-79): any of the
  * output pointers may be NULL. head_ptr_host receives nhead+1 ints. */
 int et_row_weight_meta(const et_row_weight* w, int* nrow, int* row_id_size, const int** row_id_dev,
