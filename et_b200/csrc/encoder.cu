@@ -133,6 +133,7 @@ struct Encoder {
     int kind = kTile, d_model = 0, seq_len = 0, nheads = 0, d_ff = 0;
     half* buffer = nullptr;  // caller-owned scratch for run(): buffer_num * seq_len * d_model halfs (+ scores)
     TileWeight* lin[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v o mlp1 mlp2
+    TileWeight* qkv = nullptr;   // Q|K|V as one weight: one launch, one staging of the activations per CTA
     RowWeight* rq = nullptr; RowWeight* rk = nullptr; RowWeight* rv = nullptr;
     half* d_ln[4] = {nullptr, nullptr, nullptr, nullptr};  // gamma1 beta1 gamma2 beta2
     half* d_mask = nullptr;                                // [seq_len x seq_len] additive, may be null
@@ -140,6 +141,7 @@ struct Encoder {
     bool materialize_scores = false;
     ~Encoder() {
         for (auto* t : lin) tile_weight_free(t);
+        tile_weight_free(qkv);
         delete rq; delete rk; delete rv;
         for (auto* p : d_ln) cudaFree(p);
         cudaFree(d_mask);
@@ -176,7 +178,13 @@ static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch,
     int rc;
     int q_pitch = e->d_model, v_pitch = e->d_model;
     const int *qk_hp = nullptr, *v_hp = nullptr, *v_id = nullptr;
-    if (e->kind == kPruneQKV) {
+    if (e->qkv) {
+        // fused: [T x 3 d_model] over the first three scratch buffers, Q | K | V side by side
+        if ((rc = tile_linear_run(e->qkv, b0, in, T, 0, st))) return rc;
+        q_pitch = v_pitch = 3 * e->d_model;
+        b1 = b0 + e->d_model;
+        b2 = b0 + 2 * e->d_model;
+    } else if (e->kind == kPruneQKV) {
         if ((rc = tile_linear_run(e->rq->tw, b0, in, T, 0, st))) return rc;
         if ((rc = tile_linear_run(e->rk->tw, b1, in, T, 0, st))) return rc;
         q_pitch = e->rq->nrow; qk_hp = e->rq->d_head_ptr;
@@ -184,7 +192,8 @@ static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch,
         if ((rc = tile_linear_run(e->lin[0], b0, in, T, 0, st))) return rc;
         if ((rc = tile_linear_run(e->lin[1], b1, in, T, 0, st))) return rc;
     }
-    if (e->kind == kPrune || e->kind == kPruneQKV) {
+    if (e->qkv) {
+    } else if (e->kind == kPrune || e->kind == kPruneQKV) {
         if ((rc = tile_linear_run(e->rv->tw, b2, in, T, 0, st))) return rc;
         v_pitch = e->rv->nrow; v_hp = e->rv->d_head_ptr; v_id = e->rv->d_row_id;
     } else {
@@ -199,6 +208,7 @@ static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch,
     if ((rc = attention_launch(b3, b0, b1, b2, scores, q_pitch, v_pitch, qk_hp, v_id, v_hp, e->d_mask, e->seq_len,
                                cu_seqlens, valid_lens, batch, uniform_len, T, e->d_model, e->nheads, st)))
         return rc;
+    b1 = scratch + td;
     if ((rc = tile_linear_run(e->lin[3], b0, b3, T, 0, st))) return rc;
     if ((rc = et_skip_layernorm(b0, in, e->d_ln[0], e->d_ln[1], T, e->d_model, st))) return rc;
     if ((rc = tile_linear_run(e->lin[4], b1, b0, T, 1, st))) return rc;
@@ -343,6 +353,11 @@ int et_encoder_tile_create(et_encoder** out, int kind, int d_model, int seq_len,
     if (rc) return rc;
     et_tile_weight* t[6] = {q, k, v, o, mlp1, mlp2};
     if ((rc = take_tiles(e.get(), t, 0, 6, d_model))) return rc;
+    if (et::tile_weight_out_feat(e->lin[0]) == d_model && et::tile_weight_out_feat(e->lin[1]) == d_model &&
+        et::tile_weight_out_feat(e->lin[2]) == d_model) {
+        const et::TileWeight* parts[3] = {e->lin[0], e->lin[1], e->lin[2]};
+        if ((rc = et::tile_weight_concat(&e->qkv, parts, 3, 0))) return rc;
+    }
     return finish_create(out, e);
 }
 

@@ -6,16 +6,21 @@
 //   * A CTA owns a slab of 128 tokens and a chunk of up to 24 output block-rows (16 features each).
 //     Its fp32 accumulators live in tensor memory: 16 TMEM columns per block-row, 384 columns at most.
 //   * The activations are the A operand and are read from tensor memory, not shared memory: X is
-//     brought in by TMA (128-byte-swizzled 128 x 64 panels) and moved smem -> TMEM with tcgen05.cp
-//     into one of four 32-column buffers. With A in TMEM a 128x16x16 UMMA no longer pays the
-//     4 KB shared-memory read of A, which otherwise bounds small-N UMMAs to ~20 % of tensor peak.
+//     brought in by TMA (two 128-byte-swizzled 128 x 64 panels per 128-wide K chunk) and moved
+//     smem -> TMEM with tcgen05.cp into one of 2-4 64-column slots. With A in TMEM a 128x16x16 UMMA no
+//     longer pays the 4 KB shared-memory read of A, which otherwise bounds small-N UMMAs to ~20 % of peak.
 //   * Every kept tile is one UMMA  D[128 x 16] += A[128 x 16] . tile^T  (B operand = the tile in
 //     shared memory, canonical no-swizzle K-major layout). A single warp can only issue one UMMA per
 //     ~55 clocks, so eight warps issue concurrently, each owning a disjoint set of block-rows.
 //   * The weight is re-packed once, on the host, into a stream of blocks, one per (block-row chunk,
-//     64-wide K chunk): a per-warp issue list followed by the tiles already in UMMA layout. One
+//     128-wide K chunk): a per-warp issue list followed by the tiles already in UMMA layout. One
 //     cp.async.bulk brings a block into shared memory. The sparsity pattern is kept exactly.
-//   * Epilogue: tcgen05.ld, + bias, optional GELU, fp16, 32 contiguous bytes per (row, block-row).
+//   * A ring of R slots, each one shared-memory stage plus one TMEM A slot, with one barrier hop per role
+//     and chunk: producer waits slot_free -> TMA; mover waits full -> tcgen05.cp -> commit a_ready;
+//     issuers wait a_ready -> UMMAs -> commit slot_free. (A wait that follows the same thread's
+//     tcgen05.commit costs a few hundred clocks, so hops per chunk are what the loop time is made of.)
+//   * Epilogue: tcgen05.ld, + bias, optional GELU, fp16, staged in shared memory in 128-byte-swizzled
+//     64-column panels and written with TMA stores (rows beyond T and columns beyond N are clipped).
 // Every mbarrier wait is bounded; a wait that gives up records a code in the error word, the CTA
 // stops issuing, frees its tensor memory and returns.
 #include <algorithm>
@@ -34,28 +39,40 @@ namespace et {
 namespace {
 
 constexpr int kSlab = 128;          // tokens per CTA
-constexpr int kKC = 64;             // K elements per chunk = one 128-byte-swizzled panel
+constexpr int kKC = 128;            // K elements per chunk = two 128-byte-swizzled 64-column panels
+constexpr int kPanel = 64;          // columns per panel
 constexpr int kSlices = kKC / 16;   // UMMA K steps per chunk
 constexpr int kMaxNB = 24;          // block-rows per CTA (384 accumulator columns)
-constexpr int kABufs = 4;           // A buffers in tensor memory, 32 columns each
-constexpr int kACol0 = 384;         // first A column
+constexpr int kSlotCols = kKC / 2;  // TMEM columns of one A slot
+constexpr int kMaxSlots = 6;
 constexpr int kIssuers = 8;         // UMMA-issuing warps
-constexpr int kThreads = 32 * (2 + kIssuers);
-constexpr int kXStageBytes = kSlab * kKC * 2;  // 16 KB
+constexpr int kMovers = 2;          // tcgen05.cp-issuing warps, alternating chunks
+constexpr int kFirstIssuer = 1 + kMovers;
+constexpr int kThreads = 32 * (1 + kMovers + kIssuers);
+constexpr int kDirInParams = 32;    // directory entries of each chunk's first block travel as kernel parameters
+constexpr int kPanelBytes = kSlab * kPanel * 2;   // 16 KB
+constexpr int kXStageBytes = kSlab * kKC * 2;     // 32 KB
 constexpr int kHeaderBytes = 64;
-constexpr int kMaxStages = 8;
 constexpr int kSmemMax = 232448;    // 227 KB: the per-CTA opt-in limit of sm_100
-constexpr int kMaxKChunks = 512;    // in_feat up to 32768
+constexpr int kMaxKChunks = 256;    // in_feat up to 32768
 
 struct GemmParams {
     const uint2* dir;        // per (chunk, k-chunk): {offset, size} in 16-byte units
     const uint8_t* stream;   // packed blocks
     half* Y;
     const half* bias;
-    int T, N, k_chunks, nb, stage_b_bytes, num_stages, gelu;
+    int T, N, k_chunks, nb, stage_b_bytes, slots, gelu;
     int* err;
+    uint2 first[kDirInParams];   // dir[chunk][0] for chunk < kDirInParams: no global load before the first TMA
     long long* prof;         // optional per-role clock64 stamps of CTA (0,0) (ET_GEMM_PROFILE builds only)
 };
+
+// Timing experiments (never in the shipped library): -DET_GEMM_EXPERIMENT=<mask> removes one stage's work
+// while keeping every barrier hop, to see what a chunk's time is made of. 1: no weight copy, 2: no UMMAs,
+// 4: no tcgen05.cp, 8: no activation TMA.
+#ifndef ET_GEMM_EXPERIMENT
+#define ET_GEMM_EXPERIMENT 0
+#endif
 
 #ifdef ET_GEMM_PROFILE
 #define ET_STAMP(slot) do { if (p.prof && blockIdx.x == 0 && blockIdx.y == 0) p.prof[(slot)] = clock64(); } while (0)
@@ -89,226 +106,299 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 }
 
 struct Shared {
-    uint64_t full[kMaxStages];        // stage filled (TMA X panel + weight block)
-    uint64_t stage_free[kMaxStages];  // 1 mover + 8 issuer commits
-    uint64_t a_ready[kABufs];         // A buffer holds this chunk's activations
-    uint64_t a_free[kABufs];          // 8 issuer commits
-    uint64_t acc_done;                // 8 issuer commits after the last chunk
+    uint64_t full[kMaxSlots];       // slot filled: two activation panels + the weight block (TMA)
+    uint64_t a_ready[kMaxSlots];    // the slot's activations are in tensor memory (mover commit)
+    uint64_t slot_free[kMaxSlots];  // every issuer's UMMAs on the slot have completed (8 commits)
+    uint64_t acc_done;              // 8 issuer commits after the last chunk
     uint32_t tmem_base;
     volatile int abort;
-    uint2 dir[kMaxKChunks];           // this CTA's row of the block directory
+    uint2 dir[kMaxKChunks];                // this CTA's row of the block directory
+    __align__(16) half bias[kMaxNB * 16];  // this chunk's bias
 };
 
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
-tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
+tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
+                 const __grid_constant__ GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int stage_bytes = kXStageBytes + p.stage_b_bytes;  // multiple of 1024
-    Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)p.num_stages * stage_bytes);
+    const int slot_bytes = kXStageBytes + p.stage_b_bytes;   // multiple of 1024
+    const int ring_bytes = max(p.slots * slot_bytes, ((p.nb + 3) / 4) * kPanelBytes);
+    Shared* sh = reinterpret_cast<Shared*>(smem + ring_bytes);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int slab = blockIdx.x, chunk = blockIdx.y;
-    const int S = p.num_stages;
+    const int R = p.slots;
+    const uint32_t a_col0 = 512u - (uint32_t)(R * kSlotCols);
     if (tid == 0) ET_STAMP(0);
 
-    if (tid == 0) {
-        for (int s = 0; s < S; ++s) {
-            mbar_init(&sh->full[s], 1);
-            mbar_init(&sh->stage_free[s], 1 + kIssuers);
-        }
-        for (int j = 0; j < kABufs; ++j) {
-            mbar_init(&sh->a_ready[j], 1);
-            mbar_init(&sh->a_free[j], kIssuers);
-        }
-        mbar_init(&sh->acc_done, kIssuers);
-        sh->abort = 0;
-        fence_mbar_init();
-        prefetch_tmap(&tmX);
-    }
-    if (warp == 1) {
-        tmem_alloc(&sh->tmem_base, 512);
-        tmem_relinquish();
-    } else if (warp == 0) {
-        const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
-        for (int i = lane; i < p.k_chunks; i += 32) sh->dir[i] = __ldg(gdir + i);
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sh->tmem_base;
-    if (tid == 0) ET_STAMP(1);
-
-    // Accumulators start at zero: block-rows without tiles are legal and every UMMA accumulates.
-    if (warp >= 2) {
-        const int w = warp - 2;
-        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-        for (int br = (w >> 2); br < p.nb; br += 2) tmem_st16_zero(tmem + lane_base + br * 16);
-        tmem_st_wait();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-
-    if (tid == 0) ET_STAMP(2);
-
     if (warp == 0) {
-        // ---------------- producer: TMA activations + bulk copy of the weight block
-        if (lane == 0) {
-            int issued = 0;
-            for (int kc = 0; kc < p.k_chunks; ++kc) {
-                const int s = kc % S;
-                const uint32_t ph = (uint32_t)(kc / S) & 1u;
-                const uint2 d = sh->dir[kc];
-                if (sh->abort) break;
-                const bool free_ok = mbar_wait(&sh->stage_free[s], ph ^ 1u);
-                ET_STAMP(900 + kc);
-                if (!free_ok) {
+        // ---------------- producer warp: starts at once; the other warps set up tensor memory meanwhile.
+        // Lane 0 issues the copies, lane 1 polls slot_free (a wait by the thread that has just issued a
+        // bulk copy costs several hundred clocks), lanes 2.. fetch this CTA's row of the directory.
+        {
+            const int nbar = 3 * R + 1;   // one barrier per lane
+            if (lane < nbar) {
+                if (lane < R) mbar_init(&sh->full[lane], 1);
+                else if (lane < 2 * R) mbar_init(&sh->a_ready[lane - R], 1);
+                else if (lane < 3 * R) mbar_init(&sh->slot_free[lane - 2 * R], kIssuers);
+                else mbar_init(&sh->acc_done, kIssuers);
+                fence_mbar_init();
+            }
+            if (lane == 0) sh->abort = 0;
+        }
+        __syncwarp();
+        named_barrier_arrive(2, kThreads);   // barriers are initialised: release the other warps
+        if (lane == 0) ET_STAMP(8);
+        // directory loads are issued now and only consumed at the rendezvous below, so nobody waits on them here
+        const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
+        uint2 pre[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = lane - 2 + 30 * j;
+            pre[j] = (lane >= 2 && i < p.k_chunks) ? __ldg(gdir + i) : make_uint2(0, 0);
+        }
+        int issued = 0, r = 0;
+        uint32_t ph = 0;
+        bool dir_ready = false;   // warp-level rendezvous with the lanes that loaded the directory
+        bool alive = true;
+        for (int kc = 0; kc < p.k_chunks && alive; ++kc) {
+            int go = 1;
+            if (lane == 1) go = (!sh->abort && mbar_wait(&sh->slot_free[r], ph ^ 1u)) ? 1 : 0;
+            go = __shfl_sync(0xffffffffu, go, 1);
+            if (lane == 0) ET_STAMP(900 + kc);
+            if (!go) {
+                if (lane == 0 && !sh->abort) {
                     atomicExch(p.err, 11);
                     sh->abort = 1;
-                    break;
                 }
-                uint8_t* st = smem + (size_t)s * stage_bytes;
-                const uint32_t bbytes = d.y * 16u;
-                mbar_expect_tx(&sh->full[s], kXStageBytes + bbytes);
-                ET_STAMP(1000 + kc);
-                tma_load_2d(st, &tmX, kc * kKC, slab * kSlab, &sh->full[s]);
-                ET_STAMP(1100 + kc);
-                bulk_load(st + kXStageBytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[s]);
-                ET_STAMP(100 + kc);
-                ++issued;
+                alive = false;
+                break;
             }
-            // Leaving early: wait (bounded) for the copies still in flight before the CTA exits.
-            if (sh->abort)
-                for (int kk = issued > S ? issued - S : 0; kk < issued; ++kk)
-                    mbar_wait(&sh->full[kk % S], (uint32_t)(kk / S) & 1u);
+            const bool need_dir = !(kc == 0 && chunk < kDirInParams);
+            if (need_dir && !dir_ready) {
+                // the activation copy does not need the directory: it goes out before the rendezvous
+                if (lane == 0) {
+                    mbar_expect_tx_only(&sh->full[r], kXStageBytes);
+                    tma_load_3d(smem + (size_t)r * slot_bytes, &tmX, 0, slab * kSlab, kc * (kKC / kPanel), &sh->full[r]);
+                }
+                if (lane >= 2) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int i = lane - 2 + 30 * j;
+                        if (i < p.k_chunks) sh->dir[i] = pre[j];
+                    }
+                    for (int i = lane - 2 + 120; i < p.k_chunks; i += 30) sh->dir[i] = __ldg(gdir + i);
+                }
+                __syncwarp();
+                dir_ready = true;
+                if (lane == 0) {
+                    const uint2 d = sh->dir[kc];
+                    mbar_expect_tx(&sh->full[r], d.y * 16u);
+                    bulk_load(smem + (size_t)r * slot_bytes + kXStageBytes, p.stream + (size_t)d.x * 16u, d.y * 16u,
+                              &sh->full[r]);
+                    ET_STAMP(100 + kc);
+                }
+            } else if (lane == 0) {
+                uint8_t* st = smem + (size_t)r * slot_bytes;
+                const uint2 d = need_dir ? sh->dir[kc] : p.first[chunk];
+                const uint32_t bbytes = d.y * 16u;
+                if (ET_GEMM_EXPERIMENT & 9) {
+                    const uint32_t xb = (ET_GEMM_EXPERIMENT & 8) ? 0u : (uint32_t)kXStageBytes;
+                    const uint32_t wb = (ET_GEMM_EXPERIMENT & 1) ? (uint32_t)kHeaderBytes : bbytes;
+                    mbar_expect_tx(&sh->full[r], xb + wb);
+                    if (!(ET_GEMM_EXPERIMENT & 8)) tma_load_3d(st, &tmX, 0, slab * kSlab, kc * (kKC / kPanel), &sh->full[r]);
+                    bulk_load(st + kXStageBytes, p.stream + (size_t)d.x * 16u, wb, &sh->full[r]);
+                } else {
+                mbar_expect_tx(&sh->full[r], kXStageBytes + bbytes);
+                tma_load_3d(st, &tmX, 0, slab * kSlab, kc * (kKC / kPanel), &sh->full[r]);   // both panels, one op
+                bulk_load(st + kXStageBytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[r]);
+                }
+                ET_STAMP(100 + kc);
+            }
+            ++issued;
+            if (++r == R) { r = 0; ph ^= 1u; }
         }
-    } else if (warp == 1) {
-        // ---------------- mover: shared memory -> tensor memory copy of the A operand
-        if (lane == 0) {
-            for (int kc = 0; kc < p.k_chunks; ++kc) {
-                const int s = kc % S, j = kc % kABufs;
+        if (!dir_ready) __syncwarp();
+        // Leaving early: wait (bounded) for the copies still in flight before the CTA exits.
+        if (lane == 1 && sh->abort)
+            for (int kk = issued > R ? issued - R : 0; kk < issued; ++kk)
+                mbar_wait(&sh->full[kk % R], (uint32_t)(kk / R) & 1u);
+    } else {
+        if (warp == 1) {
+            tmem_alloc(&sh->tmem_base, 512);
+            tmem_relinquish();
+        } else if (warp >= kFirstIssuer) {
+            // this chunk's bias, read again by the epilogue
+            const int col0 = chunk * p.nb * 16;
+            for (int i = tid - 32 * kFirstIssuer; i < p.nb * 16; i += 32 * kIssuers)
+                sh->bias[i] = (col0 + i < p.N) ? p.bias[col0 + i] : __float2half(0.f);
+        }
+        tc_fence_before();
+        named_barrier_sync(1, kThreads - 32);   // all but the producer: tensor-memory base and bias are visible
+        tc_fence_after();
+        const uint32_t tmem = sh->tmem_base;
+        // Accumulators start at zero: block-rows without tiles are legal and every UMMA accumulates.
+        if (warp >= kFirstIssuer) {
+            const int w = warp - kFirstIssuer;
+            const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+            for (int br = (w >> 2); br < p.nb; br += 2) tmem_st16_zero(tmem + lane_base + br * 16);
+            tmem_st_wait();
+        }
+        tc_fence_before();
+        named_barrier_sync(2, kThreads);        // + the producer's arrive: mbarriers are initialised
+        tc_fence_after();
+        if (tid == 32) ET_STAMP(2);
+
+        if (warp < kFirstIssuer) {
+            // ---------------- movers: shared memory -> tensor memory copy of the A operand. Two warps take
+            // alternate chunks, so a warp's next wait does not directly follow its own tcgen05.commit.
+            // Lane 1 polls, lane 0 issues and commits: a wait by the thread that has just committed is slow.
+            const int m = warp - 1;
+            for (int kc = m; kc < p.k_chunks; kc += kMovers) {
+                const int r = kc % R;
+                const uint32_t ph = (uint32_t)(kc / R) & 1u;
                 if (sh->abort) break;
-                bool got = mbar_wait(&sh->full[s], (uint32_t)(kc / S) & 1u);
-                ET_STAMP(700 + kc);
-                got = got && mbar_wait(&sh->a_free[j], ((uint32_t)(kc / kABufs) & 1u) ^ 1u);
-                ET_STAMP(800 + kc);
+                int got = 1;
+                if (lane == 1) got = mbar_wait(&sh->full[r], ph);
+                got = __shfl_sync(0xffffffffu, got, 1);
+                if (m == 0 && lane == 0) ET_STAMP(700 + kc);
                 if (!got) {
-                    atomicExch(p.err, 12);
+                    if (lane == 0) atomicExch(p.err, 12);
                     sh->abort = 1;
                     break;
                 }
                 tc_fence_after();
-                ET_STAMP(200 + kc);
-                const uint32_t xa = smem_u32(smem + (size_t)s * stage_bytes);
+                if (lane == 0) {
+                    const uint32_t xa = smem_u32(smem + (size_t)r * slot_bytes);
+                    const uint32_t ta = tmem + a_col0 + r * kSlotCols;
 #pragma unroll
-                for (int sl = 0; sl < kSlices; ++sl)
-                    tc_cp_128x256b(tmem + kACol0 + j * 32 + sl * 8,
-                                   make_smem_desc(xa + sl * 32, 16, 1024, 2));
-                umma_commit(&sh->a_ready[j]);
-                umma_commit(&sh->stage_free[s]);
-                ET_STAMP(300 + kc);
+                    for (int sl = 0; sl < ((ET_GEMM_EXPERIMENT & 4) ? 0 : kSlices); ++sl)
+                        tc_cp_128x256b(ta + sl * 8,
+                                       make_smem_desc(xa + (sl >> 2) * kPanelBytes + (sl & 3) * 32, 16, 1024, 2));
+                    umma_commit(&sh->a_ready[r]);
+                    if (m == 0) ET_STAMP(300 + kc);
+                }
+                __syncwarp();
             }
-        }
-    } else {
-        // ---------------- issuers: one UMMA per kept tile, A from tensor memory
-        const int w = warp - 2;
-        // B tile descriptor: no swizzle, 128 B between core matrices along K, 256 B along N.
-        const uint64_t b_desc0 = make_smem_desc(0, 128, 256, 0);
-        bool ok = true;
-        for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
-            const int s = kc % S, j = kc % kABufs;
-            if (sh->abort) { ok = false; break; }
-            // one lane polls; 256 threads spinning on the same mbarrier words slow every other
-            // barrier operation of the CTA (TMA completion included)
-            int got = 1;
-            if (lane == 0) {
-                got = mbar_wait(&sh->full[s], (uint32_t)(kc / S) & 1u);
-                if (w == 0) ET_STAMP(400 + kc);
-                got = got && mbar_wait(&sh->a_ready[j], (uint32_t)(kc / kABufs) & 1u);
-                if (w == 0) ET_STAMP(500 + kc);
-            }
-            got = __shfl_sync(0xffffffffu, got, 0);
-            if (!got) {
-                if (lane == 0) atomicExch(p.err, 13);
-                sh->abort = 1;
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            const uint8_t* blk = smem + (size_t)s * stage_bytes + kXStageBytes;
-            const uint32_t hw = reinterpret_cast<const uint32_t*>(blk)[w];
-            const int e0 = hw & 0xffff, ne = hw >> 16;
-            const uint32_t n_entries = reinterpret_cast<const uint32_t*>(blk)[8];
-            const uint4* ent = reinterpret_cast<const uint4*>(blk + kHeaderBytes) + e0;
-            const uint32_t tiles16 = (smem_u32(blk) + kHeaderBytes + n_entries * 16u) >> 4;
-            const uint32_t abuf = tmem + kACol0 + j * 32;
+        } else {
+            // ---------------- issuers: one UMMA per kept tile, A from tensor memory
+            const int w = warp - kFirstIssuer;
+            // B tile descriptor: no swizzle, 128 B between core matrices along K, 256 B along N.
+            const uint64_t b_desc0 = make_smem_desc(0, 128, 256, 0);
+            bool ok = true;
+            int r = 0;
+            uint32_t ph = 0;
+            for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
+                if (sh->abort) { ok = false; break; }
+                // a_ready implies full: the mover waited for the slot's TMA before copying. One lane polls.
+                int got = 1;
+                if (lane == 1) {
+                    got = mbar_wait(&sh->a_ready[r], ph);
+                    if (w == 0) ET_STAMP(500 + kc);
+                }
+                got = __shfl_sync(0xffffffffu, got, 1);
+                if (!got) {
+                    if (lane == 0) atomicExch(p.err, 13);
+                    sh->abort = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint8_t* blk = smem + (size_t)r * slot_bytes + kXStageBytes;
+                const uint32_t hw = reinterpret_cast<const uint32_t*>(blk)[w];
+                const int e0 = hw & 0xffff, ne = hw >> 16;
+                const uint32_t n_entries = reinterpret_cast<const uint32_t*>(blk)[8];
+                const uint4* ent = reinterpret_cast<const uint4*>(blk + kHeaderBytes) + e0;
+                const uint32_t tiles16 = (smem_u32(blk) + kHeaderBytes + n_entries * 16u) >> 4;
+                const uint32_t abuf = tmem + a_col0 + r * kSlotCols;
 #pragma unroll 4
-            for (int i = 0; i < ne; ++i) {
-                const uint4 e = ent[i];
-                if (elect_one())
-                    umma_f16_ts(tmem + e.z, abuf + e.y,
-                                b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
+                for (int i = 0; i < ne; ++i) {
+                    const uint4 e = ent[i];
+                    if (!(ET_GEMM_EXPERIMENT & 2) && elect_one())
+                        umma_f16_ts(tmem + e.z, abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
+                }
+                if (elect_one()) umma_commit(&sh->slot_free[r]);
+                if (w == 0 && lane == 0) ET_STAMP(600 + kc);
+                __syncwarp();
+                if (++r == R) { r = 0; ph ^= 1u; }
             }
-            if (elect_one()) {
-                umma_commit(&sh->stage_free[s]);
-                umma_commit(&sh->a_free[j]);
-            }
-            if (w == 0 && lane == 0) ET_STAMP(600 + kc);
+            if (elect_one()) umma_commit(&sh->acc_done);
             __syncwarp();
-        }
-        if (elect_one()) umma_commit(&sh->acc_done);
-        __syncwarp();
 
-        // ---------------- epilogue: TMEM -> registers -> bias / GELU -> fp16 -> global
-        if (ok) {
-            int done = 1;
-            if (lane == 0) done = mbar_wait(&sh->acc_done, 0);
-            done = __shfl_sync(0xffffffffu, done, 0);
-            if (!done) {
-                if (lane == 0) atomicExch(p.err, 14);
-                ok = false;
-            }
-        }
-        tc_fence_after();
-        if (w == 0 && lane == 0) ET_STAMP(3);
-        if (ok) {
-            const int q = warp & 3;
-            const int row = slab * kSlab + q * 32 + lane;
-            const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-            for (int lb = (w >> 2); lb < p.nb; lb += 2) {
-                const int col = (chunk * p.nb + lb) * 16;
-                if (col >= p.N) break;
-                uint32_t r[16];
-                tmem_ld16(tmem + lane_base + lb * 16, r);
-                tmem_ld_wait();
-                if (row < p.T) {
-                    const uint4* b4 = reinterpret_cast<const uint4*>(p.bias + col);
-                    uint4 bv[2] = {__ldg(b4), __ldg(b4 + 1)};
-                    const half2* bh = reinterpret_cast<const half2*>(bv);
-                    uint4 ov[2];
-                    half2* oh = reinterpret_cast<half2*>(ov);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float2 bb = __half22float2(bh[i]);
-                        float v0 = __uint_as_float(r[2 * i]) + bb.x;
-                        float v1 = __uint_as_float(r[2 * i + 1]) + bb.y;
-                        if (p.gelu) {
-                            v0 = gelu_tanh(v0);
-                            v1 = gelu_tanh(v1);
-                        }
-                        oh[i] = __floats2half2_rn(v0, v1);
-                    }
-                    uint4* dst = reinterpret_cast<uint4*>(p.Y + (size_t)row * p.N + col);
-                    dst[0] = ov[0];
-                    dst[1] = ov[1];
+            // ---------------- epilogue: TMEM -> registers -> bias / GELU -> fp16 -> swizzled panels -> TMA store.
+            // One round fills one 64-column panel (4 block-rows: two per column half); the panel is stored
+            // while the next round reads tensor memory.
+            if (ok) {
+                int done = 1;
+                if (lane == 0) done = mbar_wait(&sh->acc_done, 0);
+                done = __shfl_sync(0xffffffffu, done, 0);
+                if (!done) {
+                    if (lane == 0) atomicExch(p.err, 14);
+                    sh->abort = 1;
+                    ok = false;
                 }
             }
+            tc_fence_after();
+            if (w == 0 && lane == 0) ET_STAMP(3);
+            const int q = warp & 3;
+            const int row = q * 32 + lane;                 // row of the slab = TMEM lane
+            const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+            const int npanels = (p.nb + 3) >> 2;
+            for (int pi = 0; pi < npanels; ++pi) {
+                const int lb = pi * 4 + (w >> 2), lb2 = lb + 2;
+                if (ok && lb < p.nb) {
+                    const bool has2 = lb2 < p.nb;
+                    uint32_t acc[2][16];
+                    tmem_ld16(tmem + lane_base + lb * 16, acc[0]);
+                    if (has2) tmem_ld16(tmem + lane_base + lb2 * 16, acc[1]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        if (u == 1 && !has2) break;
+                        const int l = u ? lb2 : lb;
+                        const half2* bh = reinterpret_cast<const half2*>(sh->bias + l * 16);
+                        uint4 ov[2];
+                        half2* oh = reinterpret_cast<half2*>(ov);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 bb = __half22float2(bh[i]);
+                            float v0 = __uint_as_float(acc[u][2 * i]) + bb.x;
+                            float v1 = __uint_as_float(acc[u][2 * i + 1]) + bb.y;
+                            if (p.gelu) {
+                                v0 = gelu_tanh(v0);
+                                v1 = gelu_tanh(v1);
+                            }
+                            oh[i] = __floats2half2_rn(v0, v1);
+                        }
+                        // 16-byte chunks 2*(l%4) and 2*(l%4)+1 of the row, 128-byte swizzle
+                        uint8_t* prow = smem + (size_t)pi * kPanelBytes + row * 128;
+                        const int c0 = (l & 3) * 2;
+                        *reinterpret_cast<uint4*>(prow + (((c0) ^ (row & 7)) << 4)) = ov[0];
+                        *reinterpret_cast<uint4*>(prow + (((c0 + 1) ^ (row & 7)) << 4)) = ov[1];
+                    }
+                    fence_proxy_async_smem();
+                }
+                named_barrier_sync(3, 32 * kIssuers);   // the panel is complete
+                if (w == 0 && lane == 0 && !sh->abort) {
+                    const int col = chunk * p.nb * 16 + pi * kPanel;
+                    if (col < p.N) tma_store_2d(&tmY, smem + (size_t)pi * kPanelBytes, col, slab * kSlab);
+                    tma_store_commit();
+                }
+            }
+            if (w == 0 && lane == 0) tma_store_wait_read();   // shared memory may go once the stores have read it
         }
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     if (tid == 0) ET_STAMP(4);
-    if (warp == 1) tmem_dealloc(tmem, 512);
+    if (warp == 1) tmem_dealloc(sh->tmem_base, 512);
 }
 
 }  // namespace
@@ -316,8 +406,13 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
 // --------------------------------------------------------------------------------- host side
 
 struct TileWeight {
-    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, num_stages = 0;
+    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, slots = 0;
     long ntile = 0;
+    int size_hint = 0;
+    // the caller's arrays, kept so that weights can be concatenated (Q|K|V in one launch) and re-packed
+    std::vector<int> h_row_ptr, h_row_offset;
+    std::vector<half> h_data, h_bias;
+    std::vector<uint2> h_first;   // directory entry of each chunk's first block
     uint2* d_dir = nullptr;
     uint8_t* d_stream = nullptr;
     half* d_bias = nullptr;
@@ -325,14 +420,24 @@ struct TileWeight {
     size_t stream_bytes = 0;
 };
 
-static int choose_nb(int n_block_rows, int size_hint) {
+// Block-rows per CTA. The kernel is bound by what one SM can pull from L2 (the 16 KB activation panel plus
+// the weight block per K chunk), so the estimate is waves x bytes per K chunk; ties go to the larger chunk
+// (fewer passes over the activations).
+static int choose_nb(int n_block_rows, int size_hint, double density) {
     const int slabs = std::max(1, (size_hint + kSlab - 1) / kSlab);
-    const int target = sm_count() * 9 / 10;
+    const int sms = std::max(1, sm_count());
+    double best = 0;
+    int best_nb = 0;
     for (int nb : {24, 16, 12, 8}) {
-        const int chunks = (n_block_rows + nb - 1) / nb;
-        if ((long)slabs * chunks >= target) return std::min(nb, std::max(n_block_rows, 1));
+        // chunks other than a single one must cover whole 64-column output panels (nb % 4 == 0)
+        const int nbe = n_block_rows <= nb ? std::max(n_block_rows, 1) : nb;
+        if (nbe > kMaxNB) continue;
+        const long ctas = (long)slabs * ((n_block_rows + nbe - 1) / nbe);
+        const double waves = (double)((ctas + sms - 1) / sms);
+        const double cost = waves * (kXStageBytes + nbe * kSlices * density * 528.0 + 4096.0);
+        if (best_nb == 0 || cost < best * 0.999) { best = cost; best_nb = nbe; }
     }
-    return std::min(8, std::max(n_block_rows, 1));
+    return best_nb;
 }
 
 int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, const half* data,
@@ -349,8 +454,18 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
         if (row_offset[i] < 0 || row_offset[i] % 16 || row_offset[i] + 16 > K) return fail(ET_ERR_INVALID, "tile weight: row_offset out of range or not a multiple of 16");
 
     auto* w = new TileWeight();
-    w->K = K; w->N = N; w->ntile = ntile;
-    w->nb = nb_override > 0 ? std::min(nb_override, kMaxNB) : choose_nb(NBR, size_hint);
+    w->K = K; w->N = N; w->ntile = ntile; w->size_hint = size_hint;
+    const double density = (double)ntile / std::max(1.0, (double)NBR * (K / 16));
+    w->nb = choose_nb(NBR, size_hint, density);
+    if (nb_override > 0) {
+        const int nbo = std::min(nb_override, kMaxNB);
+        w->nb = NBR <= nbo ? NBR : std::max(4, nbo / 4 * 4);
+    }
+    w->h_row_ptr.assign(row_ptr, row_ptr + NBR + 1);
+    w->h_row_offset.assign(row_offset, row_offset + ntile);
+    w->h_data.assign(data, data + (size_t)ntile * 256);
+    w->h_bias.assign((size_t)N, __float2half(0.f));
+    if (bias) std::copy(bias, bias + N, w->h_bias.begin());
     w->n_chunks = (NBR + w->nb - 1) / w->nb;
     w->k_chunks = (K + kKC - 1) / kKC;
     if (w->k_chunks > kMaxKChunks) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: in_feat above 32768"); }
@@ -400,11 +515,12 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
         dir[b] = make_uint2((uint32_t)(off / 16), (uint32_t)(bytes / 16));
         max_block = std::max(max_block, bytes);
     }
+    for (int c = 0; c < w->n_chunks && c < kDirInParams; ++c) w->h_first.push_back(dir[(size_t)c * w->k_chunks]);
     w->stage_b_bytes = (int)((max_block + 1023) / 1024 * 1024);
-    const int stage = kXStageBytes + w->stage_b_bytes;
-    w->num_stages = std::min(kMaxStages, (kSmemMax - 1024 - (int)sizeof(Shared)) / stage);
-    if (w->num_stages < 2) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
-    w->num_stages = std::min(w->num_stages, std::max(2, w->k_chunks));
+    const int slot = kXStageBytes + w->stage_b_bytes;
+    const int tmem_slots = (512 - w->nb * 16) / kSlotCols;
+    w->slots = std::min({kMaxSlots, tmem_slots, (kSmemMax - 1024 - (int)sizeof(Shared)) / slot});
+    if (w->slots < 2) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
     w->stream_bytes = stream.size();
 
     cudaError_t e1 = cudaMalloc(&w->d_dir, dir.size() * sizeof(uint2));
@@ -421,6 +537,26 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     if (rc) { tile_weight_free(w); return rc; }
     *out = w;
     return ET_OK;
+}
+
+// One weight whose output features are those of `parts` back to back (same in_feat): Q|K|V in one launch.
+int tile_weight_concat(TileWeight** out, const TileWeight* const* parts, int count, int size_hint) {
+    if (!out || !parts || count <= 0) return fail(ET_ERR_INVALID, "tile weight concat: bad arguments");
+    std::vector<int> rp(1, 0), ro;
+    std::vector<half> data, bias;
+    int N = 0;
+    for (int i = 0; i < count; ++i) {
+        const TileWeight* w = parts[i];
+        if (!w || w->K != parts[0]->K) return fail(ET_ERR_INVALID, "tile weight concat: in_feat differs");
+        const int base = rp.back();
+        for (size_t r = 1; r < w->h_row_ptr.size(); ++r) rp.push_back(base + w->h_row_ptr[r]);
+        ro.insert(ro.end(), w->h_row_offset.begin(), w->h_row_offset.end());
+        data.insert(data.end(), w->h_data.begin(), w->h_data.end());
+        bias.insert(bias.end(), w->h_bias.begin(), w->h_bias.end());
+        N += w->N;
+    }
+    return tile_weight_pack(out, parts[0]->K, N, size_hint > 0 ? size_hint : parts[0]->size_hint, (long)ro.size(), data.data(), rp.data(), ro.data(),
+                            bias.data(), 0);
 }
 
 void tile_weight_free(TileWeight* w) {
@@ -441,8 +577,9 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     if (T < 0) return fail(ET_ERR_INVALID, "tile linear: negative token count");
     if (T == 0) return ET_OK;
     if (!aligned16(X) || !aligned16(Y)) return fail(ET_ERR_INVALID, "tile linear: X and Y must be 16-byte aligned");
-    CUtensorMap tm;
-    if (!make_tmap_2d_f16(&tm, X, (uint64_t)T, (uint64_t)w->K, (uint64_t)w->K, kSlab, kKC, true))
+    CUtensorMap tm, tmy;
+    if (!make_tmap_panels_f16(&tm, X, (uint64_t)T, (uint64_t)w->K, (uint64_t)w->K, kSlab, kKC / kPanel) ||
+        !make_tmap_2d_f16(&tmy, Y, (uint64_t)T, (uint64_t)w->N, (uint64_t)w->N, kSlab, kPanel, true))
         return fail(ET_ERR_CUDA, "tile linear: cuTensorMapEncodeTiled failed");
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
@@ -453,13 +590,18 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     GemmParams p;
     p.dir = w->d_dir; p.stream = w->d_stream; p.Y = Y; p.bias = w->d_bias;
     p.T = T; p.N = w->N; p.k_chunks = w->k_chunks; p.nb = w->nb;
-    p.stage_b_bytes = w->stage_b_bytes; p.num_stages = w->num_stages; p.gelu = gelu; p.err = w->d_err;
+    p.stage_b_bytes = w->stage_b_bytes; p.slots = w->slots; p.gelu = gelu; p.err = w->d_err;
     p.prof = g_prof;
-    const size_t smem = (size_t)w->num_stages * (kXStageBytes + w->stage_b_bytes) + sizeof(Shared) + 1024;
+    for (size_t c = 0; c < w->h_first.size(); ++c) p.first[c] = w->h_first[c];
+    const size_t ring = std::max<size_t>((size_t)w->slots * (kXStageBytes + w->stage_b_bytes),
+                                         (size_t)((w->nb + 3) / 4) * kPanelBytes);
+    const size_t smem = ring + sizeof(Shared) + 1024;
     dim3 grid((T + kSlab - 1) / kSlab, w->n_chunks);
-    tile_gemm_kernel<<<grid, kThreads, smem, st>>>(tm, p);
+    tile_gemm_kernel<<<grid, kThreads, smem, st>>>(tm, tmy, p);
     return cuda_status(cudaGetLastError(), "tile linear launch");
 }
+
+int tile_weight_out_feat(const TileWeight* w) { return w->N; }
 
 int tile_weight_error(const TileWeight* w, int* code) {
     int v = 0;
@@ -471,7 +613,7 @@ int tile_weight_error(const TileWeight* w, int* code) {
 }
 
 void tile_weight_info(const TileWeight* w, int* info) {
-    info[0] = w->nb; info[1] = w->n_chunks; info[2] = w->k_chunks; info[3] = w->num_stages;
+    info[0] = w->nb; info[1] = w->n_chunks; info[2] = w->k_chunks; info[3] = w->slots;
     info[4] = w->stage_b_bytes; info[5] = (int)std::min<size_t>(w->stream_bytes, 0x7fffffff);
 }
 

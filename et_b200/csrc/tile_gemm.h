@@ -11,6 +11,9 @@ struct TileWeight;
 // nb_override > 0 forces the block-rows-per-CTA choice (tests); 0 picks it from size_hint.
 int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, const half* data,
                      const int* row_ptr, const int* row_offset, const half* bias, int nb_override);
+// New weight = the parts' output features back to back (equal in_feat); the parts stay valid.
+int tile_weight_concat(TileWeight** out, const TileWeight* const* parts, int count, int size_hint);
+int tile_weight_out_feat(const TileWeight* w);
 void tile_weight_free(TileWeight* w);
 int tile_weight_set_bias_device(TileWeight* w, const half* bias_dev, cudaStream_t st);
 int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st);

@@ -42,4 +42,21 @@ inline bool make_tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, 
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same matrix seen as [cols/64 panels][rows][64 columns]: one box = `box_panels` adjacent 64-column
+// panels of `box_rows` rows, each landing as its own 128-byte-swizzled [box_rows x 64] block, back to back.
+// cols must be a multiple of 8; columns beyond `cols` in the last panel read as zero.
+inline bool make_tmap_panels_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
+                                 uint64_t pitch_elems, uint32_t box_rows, uint32_t box_panels) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const uint64_t panels = (cols + 63) / 64;
+    cuuint64_t dims[3] = {64, rows, panels};
+    cuuint64_t strides[2] = {pitch_elems * 2, 128};
+    cuuint32_t box[3] = {64, box_rows, box_panels};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace et
