@@ -83,12 +83,41 @@ __device__ __forceinline__ void load_tile(half* dst, const half* __restrict__ sr
     }
 }
 
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool pred) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int bytes = pred ? 16 : 0;   // 0: nothing is read, the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// load_tile with 16-byte asynchronous copies where the operand allows it (aligned window), else synchronous.
+__device__ __forceinline__ void load_tile_async(half* dst, const half* __restrict__ src, long row0, long row_end,
+                                                int pitch, int col0, int width, int tid) {
+    const bool vec = ((pitch & 7) == 0) && ((col0 & 7) == 0) && ((width & 7) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+    if (!vec) {
+        load_tile(dst, src, row0, row_end, pitch, col0, width, tid);
+        return;
+    }
+    for (int i = tid; i < kBK * (kD / 8); i += 128) {
+        const int r = i >> 3, c = (i & 7) * 8;
+        const bool in = row0 + r < row_end && c < width;
+        cp_async16(dst + r * kPitch + c, in ? src + (row0 + r) * pitch + col0 + c : src, in);
+    }
+}
+
 __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
     __shared__ __align__(16) half sQ[kBQ * kPitch];
-    __shared__ __align__(16) half sK[kBK * kPitch];
-    __shared__ __align__(16) half sV[kBK * kPitch];
+    __shared__ __align__(16) half sKb[2][kBK * kPitch];   // two stages: block kb+1 streams in while kb is used
+    __shared__ __align__(16) half sVb[2][kBK * kPitch];
     __shared__ int s_seq[3];  // sequence index, first token, query offset inside the sequence
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int h = blockIdx.y;
@@ -127,7 +156,16 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
     const int ksteps = (qkw + 15) >> 4;       // k16 steps of Q K^T that hold data
     const int vtiles = (vw + 7) >> 3;         // n8 tiles of P V that hold data
 
-    if (!p.scores) load_tile(sQ, p.Q, tok0 + q0, tok0 + L, p.q_pitch, qk0, qkw, tid);
+    const int nkb = (valid + kBK - 1) / kBK;
+    // Q and the first key/value block are requested together; later blocks are requested one ahead.
+    if (nkb > 0) {
+        if (!p.scores) {
+            load_tile_async(sQ, p.Q, tok0 + q0, tok0 + L, p.q_pitch, qk0, qkw, tid);
+            load_tile_async(sKb[0], p.K, tok0, tok0 + valid, p.q_pitch, qk0, qkw, tid);
+        }
+        load_tile_async(sVb[0], p.V, tok0, tok0 + valid, p.v_pitch, v0, vw, tid);
+        cp_async_commit();
+    }
     // pruned V: the head's whole Z window starts as zero, retained columns are scattered over it later
     if (p.v_head_ptr) {
         for (int i = tid; i < kBQ * hd; i += 128) {
@@ -135,29 +173,34 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
             if (q0 + r < L) p.Z[(tok0 + q0 + r) * p.z_pitch + h * hd + c] = __float2half(0.f);
         }
     }
-    __syncthreads();
 
     uint32_t qf[4][4];
-    if (!p.scores) {
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-            ldsm_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
-                    sQ + (warp * 16 + (lane & 15)) * kPitch + ks * 16 + (lane >> 4) * 8);
-    }
-
     float o[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8 of this warp's 16
     const int qr0 = q0 + warp * 16 + g, qr1 = qr0 + 8;          // query index inside the sequence
 
-    const int nkb = (valid + kBK - 1) / kBK;
     for (int kb = 0; kb < nkb; ++kb) {
         const int k0 = kb * kBK;
+        const half* sK = sKb[kb & 1];
+        const half* sV = sVb[kb & 1];
+        if (kb + 1 < nkb) {
+            if (!p.scores)
+                load_tile_async(sKb[(kb + 1) & 1], p.K, tok0 + k0 + kBK, tok0 + valid, p.q_pitch, qk0, qkw, tid);
+            load_tile_async(sVb[(kb + 1) & 1], p.V, tok0 + k0 + kBK, tok0 + valid, p.v_pitch, v0, vw, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
         __syncthreads();
-        if (!p.scores) load_tile(sK, p.K, tok0 + k0, tok0 + valid, p.q_pitch, qk0, qkw, tid);
-        load_tile(sV, p.V, tok0 + k0, tok0 + valid, p.v_pitch, v0, vw, tid);
-        __syncthreads();
+        if (kb == 0 && !p.scores) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+                ldsm_x4(qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3],
+                        sQ + (warp * 16 + (lane & 15)) * kPitch + ks * 16 + (lane >> 4) * 8);
+        }
 
         float s[8][4];
         if (!p.scores) {
@@ -249,6 +292,7 @@ __global__ void __launch_bounds__(128) attention_kernel(const AttnParams p) {
                 }
             }
         }
+        __syncthreads();   // this stage is overwritten by the request issued in the next iteration
     }
     // ---- finalize: divide by the row sum (per-thread partial sums are combined across the quad)
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -284,6 +328,8 @@ __global__ void __launch_bounds__(128) qk_scores_kernel(half* __restrict__ S, co
                                                         int nhead, int hd, float scale) {
     __shared__ __align__(16) half sQ[kBQ * kPitch];
     __shared__ __align__(16) half sK[kBK * kPitch];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int b = blockIdx.z / nhead, h = blockIdx.z % nhead;
@@ -336,8 +382,9 @@ int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, in
     if (batch == 0 || L == 0) return ET_OK;
     if ((long)batch * nhead > 65535) return fail(ET_ERR_UNSUPPORTED, "qk scores: batch*nhead above 65535");
     dim3 grid((L + kBQ - 1) / kBQ, (L + kBK - 1) / kBK, batch * nhead);
-    qk_scores_kernel<<<grid, 128, 0, st>>>(S, Q, K, L, d_model, nhead, hd, 1.0f / sqrtf((float)hd));
-    return cuda_status(cudaGetLastError(), "qk scores launch");
+    return cuda_status(launch_pdl(qk_scores_kernel, grid, dim3(128), 0, st, S, Q, K, L, d_model, nhead, hd,
+                                  1.0f / sqrtf((float)hd)),
+                       "qk scores launch");
 }
 
 int attention_launch(half* Z, const half* Q, const half* K, const half* V, const half* scores,
@@ -363,8 +410,7 @@ int attention_launch(half* Z, const half* Q, const half* K, const half* V, const
     p.scale_log2 = scores ? 1.4426950408889634f : 1.4426950408889634f / sqrtf((float)hd);
     const int nblk = cu_seqlens ? (total_tokens + kBQ - 1) / kBQ + batch
                                 : batch * ((uniform_len + kBQ - 1) / kBQ);
-    attention_kernel<<<dim3(nblk, nhead), 128, 0, st>>>(p);
-    return cuda_status(cudaGetLastError(), "attention launch");
+    return cuda_status(launch_pdl(attention_kernel, dim3(nblk, nhead), dim3(128), 0, st, p), "attention launch");
 }
 
 

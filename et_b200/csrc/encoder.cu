@@ -139,7 +139,18 @@ struct Encoder {
     half* d_mask = nullptr;                                // [seq_len x seq_len] additive, may be null
     int* d_lens = nullptr; int lens_cap = 0;               // cu_seqlens (batch+1) then valid_lens (batch)
     bool materialize_scores = false;
+    // Replay cache: one instantiated CUDA graph per distinct call (buffers, lengths). A layer is 7 short
+    // launches; replaying them as one graph removes the launch gaps between them.
+    struct Replay {
+        std::vector<int64_t> key;
+        int seen = 0;
+        cudaGraphExec_t exec = nullptr;
+    };
+    std::vector<Replay> replays;
+    bool use_graphs = true;
     ~Encoder() {
+        for (auto& r : replays)
+            if (r.exec) cudaGraphExecDestroy(r.exec);
         for (auto* t : lin) tile_weight_free(t);
         tile_weight_free(qkv);
         delete rq; delete rk; delete rv;
@@ -483,8 +494,63 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
         if (!uniform) cu = e->d_lens;
         if (valid_lens_host) vl = e->d_lens + batch + 1;
     }
-    return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in), static_cast<half*>(scratch),
-                               T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+    // First call with given buffers and lengths runs directly, the second is captured into a graph, later ones
+    // replay it. Skipped while the caller's stream is itself being captured.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (!e->use_graphs || cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
+        return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+    std::vector<int64_t> key = {(int64_t)(intptr_t)out, (int64_t)(intptr_t)in, (int64_t)(intptr_t)scratch,
+                                (int64_t)batch, (int64_t)(valid_lens_host != nullptr), (int64_t)e->materialize_scores};
+    for (int v : meta) key.push_back(v);
+    Encoder::Replay* slot = nullptr;
+    for (auto& r : e->replays)
+        if (r.key == key) slot = &r;
+    if (!slot) {
+        if (e->replays.size() >= 8) {
+            if (e->replays.front().exec) cudaGraphExecDestroy(e->replays.front().exec);
+            e->replays.erase(e->replays.begin());
+        }
+        e->replays.push_back({key, 0, nullptr});
+        slot = &e->replays.back();
+    }
+    if (slot->exec) return et::cuda_status(cudaGraphLaunch(slot->exec, st), "et_encoder_run_batch: graph launch");
+    if (slot->seen++ == 0)
+        return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+    }
+    const int frc = et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
+                                        static_cast<half*>(scratch), T, cu, vl, batch,
+                                        uniform ? seq_lens_host[0] : 0, st);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(st, &graph);
+    if (frc != ET_OK || ce != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        e->use_graphs = false;   // fall back to plain launches for this encoder
+        return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+    }
+    const cudaError_t ie = cudaGraphInstantiate(&slot->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+        slot->exec = nullptr;
+        cudaGetLastError();
+        e->use_graphs = false;
+        return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+    }
+    return et::cuda_status(cudaGraphLaunch(slot->exec, st), "et_encoder_run_batch: graph launch");
+}
+
+int et_encoder_set_graph_replay(et_encoder* enc, int on) {
+    ET_REQUIRE(enc && enc->e, "et_encoder_set_graph_replay: null encoder");
+    enc->e->use_graphs = on != 0;
+    return ET_OK;
 }
 
 }  // extern "C"

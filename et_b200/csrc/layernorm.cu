@@ -21,6 +21,8 @@ __global__ void __launch_bounds__(256, (CH <= 4 ? 3 : 1)) skip_layernorm_vec(hal
                                                           const half* __restrict__ gamma,
                                                           const half* __restrict__ beta, int num,
                                                           int size) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int nwarp = (gridDim.x * blockDim.x) >> 5;
@@ -93,6 +95,8 @@ __global__ void __launch_bounds__(256) skip_layernorm_generic(half* __restrict__
                                                               const half* __restrict__ gamma,
                                                               const half* __restrict__ beta,
                                                               int num, int size) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int nwarp = (gridDim.x * blockDim.x) >> 5;
@@ -139,16 +143,16 @@ extern "C" int et_skip_layernorm(void* in_out, const void* skip, const void* gam
     if (vec) {
         const int ch = (size / 8 + 31) / 32;
         switch (ch) {
-            case 1: skip_layernorm_vec<1><<<blocks, 256, 0, st>>>(x, s, g, b, num, size); break;
-            case 2: skip_layernorm_vec<2><<<blocks, 256, 0, st>>>(x, s, g, b, num, size); break;
-            case 3: skip_layernorm_vec<3><<<blocks, 256, 0, st>>>(x, s, g, b, num, size); break;
-            case 4: skip_layernorm_vec<4><<<blocks, 256, 0, st>>>(x, s, g, b, num, size); break;
+            case 1: launch_pdl(skip_layernorm_vec<1>, dim3(blocks), dim3(256), 0, st, x, s, g, b, num, size); break;
+            case 2: launch_pdl(skip_layernorm_vec<2>, dim3(blocks), dim3(256), 0, st, x, s, g, b, num, size); break;
+            case 3: launch_pdl(skip_layernorm_vec<3>, dim3(blocks), dim3(256), 0, st, x, s, g, b, num, size); break;
+            case 4: launch_pdl(skip_layernorm_vec<4>, dim3(blocks), dim3(256), 0, st, x, s, g, b, num, size); break;
             case 5:
-            case 6: skip_layernorm_vec<6><<<blocks, 256, 0, st>>>(x, s, g, b, num, size); break;
-            default: skip_layernorm_vec<8><<<blocks, 256, 0, st>>>(x, s, g, b, num, size); break;
+            case 6: launch_pdl(skip_layernorm_vec<6>, dim3(blocks), dim3(256), 0, st, x, s, g, b, num, size); break;
+            default: launch_pdl(skip_layernorm_vec<8>, dim3(blocks), dim3(256), 0, st, x, s, g, b, num, size); break;
         }
     } else {
-        skip_layernorm_generic<<<blocks, 256, 0, st>>>(x, s, g, b, num, size);
+        launch_pdl(skip_layernorm_generic, dim3(blocks), dim3(256), 0, st, x, s, g, b, num, size);
     }
     return cuda_status(cudaGetLastError(), "et_skip_layernorm launch");
 }

@@ -14,6 +14,8 @@ template <int CH>  // 16-byte chunks per lane; covers L <= CH*256
 __global__ void __launch_bounds__(256) softmax_mask_vec(half* __restrict__ scores,
                                                         const half* __restrict__ mask, long nrow,
                                                         int L, int valid) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long nwarp = ((long)gridDim.x * blockDim.x) >> 5;
@@ -77,6 +79,8 @@ __global__ void __launch_bounds__(256) softmax_mask_vec(half* __restrict__ score
 __global__ void __launch_bounds__(256) softmax_mask_generic(half* __restrict__ scores,
                                                             const half* __restrict__ mask,
                                                             long nrow, int L, int valid) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long nwarp = ((long)gridDim.x * blockDim.x) >> 5;
@@ -124,14 +128,14 @@ extern "C" int et_softmax_mask(void* scores, const void* mask, int nmat, int seq
     if (vec) {
         const int ch = (seq_len / 8 + 31) / 32;
         switch (ch) {
-            case 1: softmax_mask_vec<1><<<blocks, 256, 0, st>>>(s, m, nrow, seq_len, valid_len); break;
-            case 2: softmax_mask_vec<2><<<blocks, 256, 0, st>>>(s, m, nrow, seq_len, valid_len); break;
+            case 1: launch_pdl(softmax_mask_vec<1>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
+            case 2: launch_pdl(softmax_mask_vec<2>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
             case 3:
-            case 4: softmax_mask_vec<4><<<blocks, 256, 0, st>>>(s, m, nrow, seq_len, valid_len); break;
-            default: softmax_mask_vec<8><<<blocks, 256, 0, st>>>(s, m, nrow, seq_len, valid_len); break;
+            case 4: launch_pdl(softmax_mask_vec<4>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
+            default: launch_pdl(softmax_mask_vec<8>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
         }
     } else {
-        softmax_mask_generic<<<blocks, 256, 0, st>>>(s, m, nrow, seq_len, valid_len);
+        launch_pdl(softmax_mask_generic, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len);
     }
     return cuda_status(cudaGetLastError(), "et_softmax_mask launch");
 }

@@ -136,6 +136,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int R = p.slots;
     const uint32_t a_col0 = 512u - (uint32_t)(R * kSlotCols);
     if (tid == 0) ET_STAMP(0);
+    pdl_launch_dependents();   // the next kernel may set itself up on idle SMs while this one runs
 
     if (warp == 0) {
         // ---------------- producer warp: starts at once; the other warps set up tensor memory meanwhile.
@@ -155,6 +156,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         __syncwarp();
         named_barrier_arrive(2, kThreads);   // barriers are initialised: release the other warps
         if (lane == 0) ET_STAMP(8);
+        // Everything above touched only this kernel's own resources and constant weights. The activations may
+        // still be in the making: wait for the preceding kernels before the first copy (lane 0 issues them all).
+        if (lane == 0) pdl_wait();
         // directory loads are issued now and only consumed at the rendezvous below, so nobody waits on them here
         const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
         uint2 pre[4];
@@ -321,7 +325,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 for (int i = 0; i < ne; ++i) {
                     const uint4 e = ent[i];
                     if (!(ET_GEMM_EXPERIMENT & 2) && elect_one())
-                        umma_f16_ts(tmem + e.z, abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
+                        umma_f16_ts(tmem + e.z + ((ET_GEMM_EXPERIMENT & 16) ? (uint32_t)(i & 1) * 128u : 0u), abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
                 }
                 if (elect_one()) umma_commit(&sh->slot_free[r]);
                 if (w == 0 && lane == 0) ET_STAMP(600 + kc);
@@ -597,7 +601,8 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
                                          (size_t)((w->nb + 3) / 4) * kPanelBytes);
     const size_t smem = ring + sizeof(Shared) + 1024;
     dim3 grid((T + kSlab - 1) / kSlab, w->n_chunks);
-    tile_gemm_kernel<<<grid, kThreads, smem, st>>>(tm, tmy, p);
+    const cudaError_t le = launch_pdl(tile_gemm_kernel, grid, dim3(kThreads), smem, st, tm, tmy, p);
+    if (le != cudaSuccess) return cuda_status(le, "tile linear launch");
     return cuda_status(cudaGetLastError(), "tile linear launch");
 }
 

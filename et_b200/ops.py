@@ -257,6 +257,9 @@ class Encoder:
                                          stream_ptr(stream)))
         return out
 
+    def set_graph_replay(self, on):
+        check(lib().et_encoder_set_graph_replay(self._h, _i(1 if on else 0)))
+
     def set_materialize_scores(self, on):
         check(lib().et_encoder_set_materialize_scores(self._h, _i(1 if on else 0)))
 

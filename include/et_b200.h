@@ -179,6 +179,11 @@ int et_encoder_run(et_encoder* enc, void* out, const void* in, void* stream);
  * scratch: device buffer of et_encoder_batch_buffer_size bytes. */
 int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* seq_lens_host,
                          const int* valid_lens_host, int batch, void* scratch, size_t scratch_bytes, void* stream);
+/* et_encoder_run_batch replays a CUDA graph of the layer's launches from the third call on with the same
+ * buffers and lengths (no counterpart in the reference, whose run() blocks the host three times per layer).
+ * on = 0 turns that off (plain launches every call). It is skipped by itself while the caller's stream is
+ * being captured. */
+int et_encoder_set_graph_replay(et_encoder* enc, int on);
 /* Length encoder only: route attention through scores materialised in HBM (the reference's structure,
  * encoder/encoder.cu:126-136) instead of the default on-the-fly kernel. Equal-length batches only. */
 int et_encoder_set_materialize_scores(et_encoder* enc, int on);
