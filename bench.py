@@ -8,6 +8,9 @@ resident in HBM; `e2e` times the public call with pinned host buffers (H2D of th
 inside the timed region). With N ranks each rank runs its own batch (weak scaling, no collective inside the
 layer) and the output shards are gathered with one NCCL all-gather per step.
 
+Cold-cache rule: the step visits INSTANCES independent copies of the workload (own weights, activations,
+scratch; about 25 MB each, 300 MB in total) round-robin, so no step finds its inputs in the 126 MB L2.
+
 `--impl reference` runs the reference project's own CUDA kernels (library prebuilt from the reference
 checkout under oracle/_ref/) on the same workload, composed in the reference's op order; if that library is
 absent it times the fp32 CPU oracle instead.
@@ -28,8 +31,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 D_MODEL, NHEAD, D_FF, BATCH, SEQ = 768, 12, 3072, 16, 128
+T = BATCH * SEQ
 SWEEP = (0.5, 0.75, 0.9)
-L2_FLUSH_BYTES = 256 << 20
+INSTANCES = 12
+METRIC = "encoder sequences/sec (one tile-pruned BERT-base layer)"
 
 
 def peaks():
@@ -37,13 +42,12 @@ def peaks():
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"], "tflops_sustained": p.get("bf16_tflops_sustained"),
-                "source": "measured"}
-    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
 
 
 class ClockSampler:
-    """Samples nvidia-smi SM clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi SM clocks and throttle reasons while the GPU is under load."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -53,10 +57,9 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
+            threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
         return self
@@ -86,8 +89,7 @@ class ClockSampler:
                     reasons.add(n)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
 def make_layer_host(orc, sparsity, seed):
@@ -103,9 +105,9 @@ def make_layer_host(orc, sparsity, seed):
     return lin, ln
 
 
-def layer_flops(lin, tokens, batch, seq):
-    gemm = sum(2.0 * tokens * 256 * len(v[1]) for v in lin.values())
-    attn = 4.0 * seq * seq * D_MODEL * batch
+def layer_flops(lin):
+    gemm = sum(2.0 * T * 256 * len(v[1]) for v in lin.values())
+    attn = 4.0 * SEQ * SEQ * D_MODEL * BATCH
     return gemm, attn
 
 
@@ -120,21 +122,42 @@ def cpu_baseline(orc, lin, ln, X):
         if el > 10.0 or reps >= 20:
             break
     return {"value": BATCH * reps / el, "unit": "sequences/s", "cores": orc.threads(), "kind": "port",
-            "sample": f"{reps} full forwards of the {BATCH}x{SEQ} batch ({BATCH * SEQ} tokens), fp32 oracle with OpenMP"}
+            "sample": f"{reps} full forwards of the {BATCH}x{SEQ} batch ({T} tokens), fp32 oracle with OpenMP"}
 
 
-def run_reference(args, rank, world):
+def workload_config(args):
+    return {"workload": f"config 2 (encoder_tile_test): one tile-pruned BERT-base encoder layer, batch {BATCH} x seq {SEQ}, "
+                        f"hidden {D_MODEL}, {NHEAD} heads, FFN {D_FF}, Bernoulli 16x16 tile sparsity {args.sparsity} per GPU",
+            "global_batch": BATCH * args.gpus, "seq_len": SEQ, "sparsity": args.sparsity,
+            "parallelism": f"dp{args.gpus}" if args.gpus > 1 else "single",
+            "l2": f"inputs larger than L2: {INSTANCES} independent instances of the layer (weights, activations, scratch, about "
+                  f"25 MB each) visited round-robin"}
+
+
+def timed(step, steps):
+    """`steps` calls of step(i) between two CUDA events on the current stream; returns ms per step."""
+    import torch
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_reference(args, rank):
     """Reference arm: the reference's own CUDA kernels, or the CPU oracle when they are unavailable."""
     from tests import oracle_lib, util
     if rank != 0:
         return
     orc = oracle_lib.load()
     lin, ln = make_layer_host(orc, args.sparsity, seed=1234)
-    X = util.activations(99, (BATCH * SEQ, D_MODEL))
-    base = {"metric": "encoder sequences/sec (one tile-pruned BERT-base layer)", "unit": "sequences/s", "impl": "reference",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": workload_config(args)}
+    X = util.activations(99, (T, D_MODEL))
+    base = {"metric": METRIC, "unit": "sequences/s", "impl": "reference", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": workload_config(args)}
     ref = oracle_lib.load_ref()
     cpu = cpu_baseline(orc, lin, ln, X)
     try:
@@ -144,84 +167,75 @@ def run_reference(args, rank, world):
         have_gpu = False
     if ref is None or not have_gpu:
         base.update({"value": cpu["value"], "ms_per_step": 1e3 * BATCH / cpu["value"], "cpu_baseline": cpu,
-                     "reference_kind": "cpu-oracle-port",
+                     "reference_kind": "fp32 CPU oracle (the reference ships no CPU path and its CUDA library is not built here)",
                      "e2e": {"value": cpu["value"], "unit": "sequences/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
         print(json.dumps(base))
         return
     import torch
     torch.cuda.set_device(0)
-    T = BATCH * SEQ
 
     class Bsr(ctypes.Structure):
         _fields_ = [("row_ptr", ctypes.c_void_p), ("row_offset", ctypes.c_void_p), ("data", ctypes.c_void_p),
                     ("bias", ctypes.c_void_p)]
-    keep = []
-    arr = (Bsr * 6)()
-    for i, name in enumerate(["q", "k", "v", "o", "ffn1", "ffn2"]):
-        rp, ro, data, bias = lin[name][:4]
-        ts = [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in (rp, ro, data, bias)]
-        keep.append(ts)
-        arr[i] = Bsr(*[t.data_ptr() for t in ts])
-    lnd = [torch.from_numpy(a).cuda() for pair in ln for a in pair]
-    mask = torch.zeros((SEQ, SEQ), dtype=torch.float16, device="cuda")
-    x = torch.from_numpy(X).cuda()
-    out = torch.zeros_like(x)
-    buf = torch.zeros(8 * T * D_MODEL, dtype=torch.float16, device="cuda")
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+
+    class RefInstance:
+        def __init__(self, idx):
+            self.keep, self.arr = [], (Bsr * 6)()
+            for i, name in enumerate(["q", "k", "v", "o", "ffn1", "ffn2"]):
+                ts = [torch.from_numpy(np.ascontiguousarray(a)).cuda() for a in lin[name][:4]]
+                self.keep.append(ts)
+                self.arr[i] = Bsr(*[t.data_ptr() for t in ts])
+            self.lnd = [torch.from_numpy(a).cuda() for pair in ln for a in pair]
+            self.mask = torch.zeros((SEQ, SEQ), dtype=torch.float16, device="cuda")
+            self.X = util.activations(99 + 1000 * idx, (T, D_MODEL))
+            self.x = torch.from_numpy(self.X).cuda()
+            self.out = torch.zeros_like(self.x)
+            self.buf = torch.zeros(8 * T * D_MODEL, dtype=torch.float16, device="cuda")
+
+    insts = [RefInstance(i) for i in range(INSTANCES)]
     scale = ctypes.c_float(1.4426950408889634 / (D_MODEL // NHEAD) ** 0.5)   # base-2 kernel: true softmax
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    vp = ctypes.c_void_p
 
-    def step():
-        rc = ref.ref_encoder_tile_layer(ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(x.data_ptr()),
-                                        ctypes.c_void_p(buf.data_ptr()), arr, *[ctypes.c_void_p(t.data_ptr()) for t in lnd],
-                                        ctypes.c_void_p(mask.data_ptr()), BATCH, SEQ, D_MODEL, NHEAD, D_FF, scale, st)
+    def step(i):
+        it = insts[i % INSTANCES]
+        rc = ref.ref_encoder_tile_layer(vp(it.out.data_ptr()), vp(it.x.data_ptr()), vp(it.buf.data_ptr()), it.arr,
+                                        *[vp(t.data_ptr()) for t in it.lnd], vp(it.mask.data_ptr()), BATCH, SEQ,
+                                        D_MODEL, NHEAD, D_FF, scale, st)
         assert rc == 0
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize()
-    times = []
     with ClockSampler(0) as cs:
-        for _ in range(args.steps):
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); step(); e1.record()
-            torch.cuda.synchronize()
-            times.append(e0.elapsed_time(e1))
-    ms = sum(times) / len(times)
-    # end to end with host buffers
-    hx = torch.from_numpy(X).pin_memory()
-    ho = torch.empty_like(hx).pin_memory()
-    torch.cuda.synchronize()
-    t_e2e = []
-    for _ in range(args.steps):
-        flush.zero_()
+        timed(step, max(args.warmup, 300))
+        ms = timed(step, args.steps)
+    hx = [torch.from_numpy(it.X).pin_memory() for it in insts]
+    ho = [torch.empty_like(h).pin_memory() for h in hx]
+    n_e2e = min(args.steps, 300)
+
+    def e2e_step(i):
+        it = insts[i % INSTANCES]
+        it.x.copy_(hx[i % INSTANCES], non_blocking=True)
+        step(i)
+        ho[i % INSTANCES].copy_(it.out, non_blocking=True)
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        x.copy_(hx, non_blocking=True); step(); ho.copy_(out, non_blocking=True)
-        torch.cuda.synchronize()
-        t_e2e.append(time.perf_counter() - t0)
-    e2e = BATCH / (sum(t_e2e) / len(t_e2e))
-    base.update({"value": BATCH / (ms * 1e-3), "ms_per_step": ms, "cpu_baseline": cpu,
-                 "reference_kind": "reference CUDA kernels (oracle/_ref), linears+LayerNorm over all tokens, attention per sequence",
+    for i in range(INSTANCES):
+        e2e_step(i)
+    t0 = time.perf_counter()
+    for i in range(n_e2e):
+        e2e_step(i)
+    e2e = BATCH / ((time.perf_counter() - t0) / n_e2e)
+    base.update({"value": BATCH / (ms * 1e-3), "ms_per_step": ms, "us_per_layer": ms * 1e3, "cpu_baseline": cpu,
+                 "reference_kind": "the reference's CUDA kernels (oracle/_ref): linears and LayerNorms once over all tokens, "
+                                   "attention once per sequence, one stream, no host synchronisation",
                  "clocks": cs.summary(),
-                 "e2e": {"value": e2e, "unit": "sequences/s", "h2d_bytes_per_step": int(hx.numel() * 2),
-                         "d2h_bytes_per_step": int(ho.numel() * 2)}})
+                 "e2e": {"value": e2e, "unit": "sequences/s", "h2d_bytes_per_step": int(hx[0].numel() * 2),
+                         "d2h_bytes_per_step": int(ho[0].numel() * 2), "steps": n_e2e}})
     print(json.dumps(base))
-
-
-def workload_config(args):
-    return {"workload": f"config 2 (encoder_tile_test): one tile-pruned BERT-base encoder layer, batch {BATCH} x seq {SEQ}, "
-                        f"hidden {D_MODEL}, {NHEAD} heads, FFN {D_FF}, Bernoulli 16x16 tile sparsity {args.sparsity} per GPU",
-            "global_batch": BATCH * args.gpus, "seq_len": SEQ, "sparsity": args.sparsity,
-            "parallelism": f"dp{args.gpus}" if args.gpus > 1 else "single",
-            "l2": f"L2 flushed between timed steps by writing a {L2_FLUSH_BYTES >> 20} MiB buffer"}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=5000)
+    ap.add_argument("--warmup", type=int, default=3000)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--sparsity", type=float, default=0.75)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -232,7 +246,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(args, rank)
         return
 
     import torch
@@ -248,157 +262,150 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     pk = peaks()
     orc = oracle_lib.load()
-    T = BATCH * SEQ
-    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
-
-    def build(sparsity):
-        lin, ln = make_layer_host(orc, sparsity, seed=1234)
-        w = {n: et.TileWeight(v[5], v[4], T, v[2], v[0], v[1], v[3], is_gelu=(n == "ffn1")) for n, v in lin.items()}
-        enc = et.Encoder(et.KIND_TILE, D_MODEL, SEQ, NHEAD, None, w["q"], w["k"], w["v"], w["o"], w["ffn1"], w["ffn2"],
-                         (ln[0][0], ln[0][1], ln[1][0], ln[1][1]))
-        return lin, ln, enc
-
-    X = util.activations(99 + rank, (T, D_MODEL))
-    x = torch.from_numpy(X).cuda()
-    out = torch.zeros_like(x)
-    scratch = torch.zeros(et.encoder_batch_buffer_size(et.KIND_TILE, D_MODEL, T, BATCH, SEQ, NHEAD) // 2,
-                          dtype=torch.float16, device="cuda")
-    gathered = torch.zeros((world * T, D_MODEL), dtype=torch.float16, device="cuda") if world > 1 else None
     lens = [SEQ] * BATCH
+    gathered = torch.zeros((world * T, D_MODEL), dtype=torch.float16, device="cuda") if world > 1 else None
 
-    def timed_layer(enc, steps, warmup):
-        def step():
-            enc.run_batch(out, x, lens, scratch)
+    class Instance:
+        """One independent copy of the workload: its own weights, input, output and scratch."""
+        def __init__(self, sparsity, idx):
+            self.lin, self.ln = make_layer_host(orc, sparsity, seed=1234)
+            w = {n: et.TileWeight(v[5], v[4], T, v[2], v[0], v[1], v[3], is_gelu=(n == "ffn1"))
+                 for n, v in self.lin.items()}
+            self.enc = et.Encoder(et.KIND_TILE, D_MODEL, SEQ, NHEAD, None, w["q"], w["k"], w["v"], w["o"], w["ffn1"],
+                                  w["ffn2"], (self.ln[0][0], self.ln[0][1], self.ln[1][0], self.ln[1][1]))
+            self.X = util.activations(99 + rank + 1000 * idx, (T, D_MODEL))
+            self.x = torch.from_numpy(self.X).cuda()
+            self.out = torch.zeros_like(self.x)
+            self.scratch = torch.zeros(et.encoder_batch_buffer_size(et.KIND_TILE, D_MODEL, T, BATCH, SEQ, NHEAD) // 2,
+                                       dtype=torch.float16, device="cuda")
+
+    def layer_step(insts):
+        def step(i):
+            it = insts[i % len(insts)]
+            it.enc.run_batch(it.out, it.x, lens, it.scratch)
             if world > 1:
-                dist.all_gather_into_tensor(gathered, out)
-        for _ in range(warmup):
-            step()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        times = []
-        for _ in range(steps):
-            flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); step(); e1.record()
-            torch.cuda.synchronize()
-            times.append(e0.elapsed_time(e1))
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        total = torch.tensor([sum(times)], dtype=torch.float64, device="cuda")
-        if world > 1:
-            dist.all_reduce(total, op=dist.ReduceOp.MAX)
-        return total.item() / steps
+                dist.all_gather_into_tensor(gathered, it.out)
+        return step
 
-    lin, ln, enc = build(args.sparsity)
+    def measure(insts, steps, warmup):
+        step = layer_step(insts)
+        timed(step, 3 * len(insts))      # direct run, graph capture and first replay of every instance
+        timed(step, warmup)
+        if world > 1:
+            dist.barrier()
+        ms = timed(step, steps)
+        if world > 1:
+            dist.barrier()
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms
+
+    insts = [Instance(args.sparsity, i) for i in range(INSTANCES)]
+    lin, ln, X = insts[0].lin, insts[0].ln, insts[0].X
     with ClockSampler(local_rank) as cs:
-        ms = timed_layer(enc, args.steps, args.warmup)
+        ms = measure(insts, args.steps, args.warmup)
     clocks = cs.summary()
     value = BATCH * world / (ms * 1e-3)
-    gemm_flops, attn_flops = layer_flops(lin, T, BATCH, SEQ)
+    gemm_flops, attn_flops = layer_flops(lin)
 
     # ---- end to end through the public call with host buffers (H2D + layer + D2H per step)
-    hx = torch.from_numpy(X).pin_memory()
-    ho = torch.empty_like(hx).pin_memory()
-    t_e2e = []
-    for i in range(args.warmup + args.steps):
-        flush.zero_()
-        torch.cuda.synchronize()
+    hx = [torch.from_numpy(it.X).pin_memory() for it in insts]
+    ho = [torch.empty_like(h).pin_memory() for h in hx]
+    n_e2e = min(args.steps, 500)
+
+    def e2e_step(i):
+        it = insts[i % INSTANCES]
+        it.x.copy_(hx[i % INSTANCES], non_blocking=True)
+        it.enc.run_batch(it.out, it.x, lens, it.scratch)
         if world > 1:
-            dist.barrier()
-        t0 = time.perf_counter()
-        x.copy_(hx, non_blocking=True)
-        enc.run_batch(out, x, lens, scratch)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, out)
-        ho.copy_(out, non_blocking=True)
-        torch.cuda.synchronize()
-        if i >= args.warmup:
-            t_e2e.append(time.perf_counter() - t0)
-    e2e_t = torch.tensor([sum(t_e2e) / len(t_e2e)], dtype=torch.float64, device="cuda")
+            dist.all_gather_into_tensor(gathered, it.out)
+        ho[i % INSTANCES].copy_(it.out, non_blocking=True)
+        torch.cuda.synchronize()          # the caller needs the result on the host before its next batch
+    for i in range(INSTANCES):
+        e2e_step(i)
     if world > 1:
-        dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
-    e2e = {"value": BATCH * world / e2e_t.item(), "unit": "sequences/s", "h2d_bytes_per_step": int(hx.numel() * 2),
-           "d2h_bytes_per_step": int(ho.numel() * 2)}
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(n_e2e):
+        e2e_step(i)
+    e2e_s = (time.perf_counter() - t0) / n_e2e
+    if world > 1:
+        t = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = t.item()
+    e2e = {"value": BATCH * world / e2e_s, "unit": "sequences/s", "h2d_bytes_per_step": int(hx[0].numel() * 2),
+           "d2h_bytes_per_step": int(ho[0].numel() * 2), "steps": n_e2e}
 
-    # ---- roofline of the dominant kernel: the six tile-GEMM launches of the layer, timed alone
-    w6 = {n: et.TileWeight(v[5], v[4], T, v[2], v[0], v[1], v[3]) for n, v in lin.items()}
-    hbuf = torch.zeros((T, D_FF), dtype=torch.float16, device="cuda")
-    ybuf = torch.zeros((T, D_FF), dtype=torch.float16, device="cuda")
-    def gemms():
-        for n in ("q", "k", "v", "o"):
-            w6[n].run(ybuf.view(-1)[:T * D_MODEL].view(T, D_MODEL), x)
-        w6["ffn1"].run(hbuf, x, gelu=True)
-        w6["ffn2"].run(ybuf.view(-1)[:T * D_MODEL].view(T, D_MODEL), hbuf)
-    for _ in range(3):
-        gemms()
-    torch.cuda.synchronize()
-    gt = []
-    for _ in range(max(10, args.steps // 2)):
-        flush.zero_()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(); gemms(); e1.record()
-        torch.cuda.synchronize()
-        gt.append(e0.elapsed_time(e1))
-    gemm_ms = sum(gt) / len(gt)
+    # ---- roofline of the dominant kernel: the tile-GEMM launches of the layer (fused Q|K|V, output, FFN1, FFN2),
+    # timed alone through the C ABI, rotating over independent weight/activation sets (larger than L2 in total)
+    raw, st = et.lib(), et.stream_ptr()
+    sets = []
+    for it in insts:
+        w = {n: et.TileWeight(v[5], v[4], T, v[2], v[0], v[1], v[3]) for n, v in it.lin.items()}
+        qkv_rp = np.concatenate([it.lin["q"][0], it.lin["k"][0][1:] + it.lin["q"][0][-1],
+                                 it.lin["v"][0][1:] + it.lin["q"][0][-1] + it.lin["k"][0][-1]]).astype(np.int32)
+        qkv = et.TileWeight(D_MODEL, 3 * D_MODEL, T, np.concatenate([it.lin[n][2] for n in "qkv"]), qkv_rp,
+                            np.concatenate([it.lin[n][1] for n in "qkv"]), np.concatenate([it.lin[n][3] for n in "qkv"]))
+        sets.append((qkv, w["o"], w["ffn1"], w["ffn2"], it.x,
+                     torch.zeros((T, D_FF), dtype=torch.float16, device="cuda"),
+                     torch.zeros((T, D_FF), dtype=torch.float16, device="cuda")))
+
+    def gemms(i):
+        qkv, o, f1, f2, xx, hbuf, ybuf = sets[i % len(sets)]
+        raw.et_tile_linear(qkv._h, et.ptr(ybuf), et.ptr(xx), T, 0, st)
+        raw.et_tile_linear(o._h, et.ptr(hbuf), et.ptr(xx), T, 0, st)
+        raw.et_tile_linear(f1._h, et.ptr(hbuf), et.ptr(xx), T, 1, st)
+        raw.et_tile_linear(f2._h, et.ptr(ybuf), et.ptr(hbuf), T, 0, st)
+    timed(gemms, 2 * len(sets))
+    gemm_ms = timed(gemms, max(100, args.steps // 10))
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
-    roofline = {"kernel": "tile_gemm_kernel (6 launches: Q,K,V,O,FFN1,FFN2)", "bound": "tensor", "achieved": achieved,
-                "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"], "peak_source": pk["source"],
-                "flops_per_launch_set": gemm_flops, "ms_per_launch_set": gemm_ms, "traffic": None,
-                "dense_equivalent_tflops": achieved / max(1e-9, 1.0 - args.sparsity)}
+    roofline = {"kernel": "tile_gemm_kernel (4 launches per layer: fused Q|K|V, output, FFN1+GELU, FFN2)", "bound": "tensor",
+                "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                "peak_source": pk["source"] + " (bf16 burst)", "flops_per_launch_set": gemm_flops,
+                "ms_per_launch_set": gemm_ms, "traffic": None,
+                "dense_equivalent_tflops": achieved / max(1e-9, 1.0 - args.sparsity),
+                "note": "algorithmic FLOPs count kept tiles only (2*T*256*ntile); at 2048 tokens the launches are bound by "
+                        "per-CTA latency (prologue, slot-ring hops, epilogue), see DESIGN.md"}
 
-    result = {"metric": "encoder sequences/sec (one tile-pruned BERT-base layer)", "value": value, "unit": "sequences/s",
-              "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "us_per_layer": ms * 1e3,
-              "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-              "config": workload_config(args), "clocks": clocks, "e2e": e2e, "gpu_launches": 9 * args.steps,
-              "roofline": roofline,
-              "layer_tflops": (gemm_flops + attn_flops) / (ms * 1e-3) / 1e12}
+    result = {"metric": METRIC, "value": value, "unit": "sequences/s", "n_gpus": world, "steps": args.steps,
+              "warmup": args.warmup, "ms_per_step": ms, "us_per_layer": ms * 1e3, "higher_is_better": True,
+              "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+              "config": workload_config(args), "clocks": clocks, "e2e": e2e, "gpu_launches": 7 * args.steps,
+              "launches_per_step": "7: fused Q|K|V tile GEMM, attention, output tile GEMM, LayerNorm, FFN1 tile GEMM (GELU), "
+                                   "FFN2 tile GEMM, LayerNorm; replayed as one CUDA graph",
+              "roofline": roofline, "layer_tflops": (gemm_flops + attn_flops) / (ms * 1e-3) / 1e12}
 
-    if rank == 0 and not args.no_extras:
-        extras = {}
-        # sparsity sweep of the same layer
+    if rank == 0 and not args.no_extras and world == 1:
+        sweep = {}
         for s in SWEEP:
             if abs(s - args.sparsity) < 1e-9:
-                extras[str(s)] = {"us_per_layer": ms * 1e3, "sequences_per_s": BATCH / (ms * 1e-3)}
+                sweep[str(s)] = {"us_per_layer": ms * 1e3, "sequences_per_s": BATCH / (ms * 1e-3)}
                 continue
-            _, _, e2 = build(s)
-            m2 = timed_layer(e2, max(10, args.steps // 2), 3) if world == 1 else None
-            if m2:
-                extras[str(s)] = {"us_per_layer": m2 * 1e3, "sequences_per_s": BATCH / (m2 * 1e-3)}
-        result["sweep"] = extras
+            i2 = [Instance(s, i) for i in range(INSTANCES)]
+            m2 = measure(i2, max(300, args.steps // 4), 100)
+            sweep[str(s)] = {"us_per_layer": m2 * 1e3, "sequences_per_s": BATCH / (m2 * 1e-3)}
+            del i2
+        result["sweep"] = sweep
         # bandwidth kernels on inputs larger than L2
         rows, dm = 131072, 1024
         a = torch.randn((rows, dm), device="cuda").half(); b = torch.randn((rows, dm), device="cuda").half()
         g = torch.ones(dm, dtype=torch.float16, device="cuda"); be = torch.zeros(dm, dtype=torch.float16, device="cuda")
-        for _ in range(3):
-            et.skip_layernorm(a, b, g, be)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(10):
-            et.skip_layernorm(a, b, g, be)
-        e1.record(); torch.cuda.synchronize()
-        ln_ms = e0.elapsed_time(e1) / 10
+        timed(lambda i: et.skip_layernorm(a, b, g, be), 3)
+        ln_ms = timed(lambda i: et.skip_layernorm(a, b, g, be), 20)
         gbs = 6.0 * dm * rows / (ln_ms * 1e-3) / 1e9
         result["roofline_layernorm"] = {"kernel": "skip_layernorm_vec<4>", "bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"],
-                                        "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "rows": rows, "size": dm}
+                                        "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "rows": rows, "size": dm,
+                                        "bytes_per_row": 6 * dm}
         del a, b
         nmat, L = 16 * 64, 512
         S = torch.randn((nmat, L, L), device="cuda").half()
-        for _ in range(3):
-            et.softmax_mask(S)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(10):
-            et.softmax_mask(S)
-        e1.record(); torch.cuda.synchronize()
-        sm_ms = e0.elapsed_time(e1) / 10
+        timed(lambda i: et.softmax_mask(S), 3)
+        sm_ms = timed(lambda i: et.softmax_mask(S), 20)
         gbs = 4.0 * L * L * nmat / (sm_ms * 1e-3) / 1e9
         result["roofline_softmax"] = {"kernel": "softmax_mask_vec<2>", "bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"],
-                                      "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "matrices": nmat, "seq_len": L}
+                                      "unit": "GB/s", "frac": gbs / pk["hbm_gbs"], "matrices": nmat, "seq_len": L,
+                                      "bytes_per_matrix": 4 * L * L}
         del S
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         result["cpu_baseline"] = cpu_baseline(orc, lin, ln, X)

@@ -16,60 +16,77 @@ __global__ void __launch_bounds__(256) softmax_mask_vec(half* __restrict__ score
                                                         int L, int valid) {
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int R = 2;   // rows per warp and iteration: twice the bytes in flight per warp
     const int lane = threadIdx.x & 31;
     const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long nwarp = ((long)gridDim.x * blockDim.x) >> 5;
     const int nchunk = L >> 3;
     constexpr float kLog2e = 1.4426950408889634f;
-    for (long row = warp; row < nrow; row += nwarp) {
-        uint4* sr = reinterpret_cast<uint4*>(scores + row * L);
-        const int q = (int)(row % L);
-        const uint4* mr = mask ? reinterpret_cast<const uint4*>(mask + (size_t)q * L) : nullptr;
-        float v[CH][8];
-        float mx = -INFINITY;
+    for (long row0 = warp * R; row0 < nrow; row0 += nwarp * R) {
+        uint4 sv[R][CH], mv[R][CH];
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-            const int c = lane + 32 * i;
-            uint4 sv = make_uint4(0, 0, 0, 0), mv = make_uint4(0, 0, 0, 0);
-            if (c < nchunk) {
-                sv = sr[c];
-                if (mr) mv = __ldg(mr + c);
-            }
-            const half2* sh = reinterpret_cast<const half2*>(&sv);
-            const half2* mh = reinterpret_cast<const half2*>(&mv);
+        for (int r = 0; r < R; ++r) {
+            const long row = row0 + r;
+            const uint4* sr = reinterpret_cast<const uint4*>(scores + row * L);
+            const uint4* mr = mask ? reinterpret_cast<const uint4*>(mask + (size_t)(row % L) * L) : nullptr;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 a = __half22float2(sh[j]), m = __half22float2(mh[j]);
-                const int k = c * 8 + 2 * j;
-                v[i][2 * j] = (c < nchunk && k < valid) ? a.x + m.x : -INFINITY;
-                v[i][2 * j + 1] = (c < nchunk && k + 1 < valid) ? a.y + m.y : -INFINITY;
-                mx = fmaxf(mx, fmaxf(v[i][2 * j], v[i][2 * j + 1]));
+            for (int i = 0; i < CH; ++i) {
+                const int c = lane + 32 * i;
+                sv[r][i] = make_uint4(0, 0, 0, 0);
+                mv[r][i] = make_uint4(0, 0, 0, 0);
+                if (row < nrow && c < nchunk) {
+                    sv[r][i] = __ldcs(sr + c);
+                    if (mr) mv[r][i] = __ldg(mr + c);
+                }
             }
         }
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
-        const float shift = (mx == -INFINITY) ? 0.f : mx * kLog2e;
-        float sum = 0.f;
+        for (int r = 0; r < R; ++r) {
+            const long row = row0 + r;
+            float v[CH][8];
+            float mx = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < CH; ++i)
+            for (int i = 0; i < CH; ++i) {
+                const int c = lane + 32 * i;
+                const half2* sh = reinterpret_cast<const half2*>(&sv[r][i]);
+                const half2* mh = reinterpret_cast<const half2*>(&mv[r][i]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[i][j] = exp2f(v[i][j] * kLog2e - shift);
-                sum += v[i][j];
+                for (int j = 0; j < 4; ++j) {
+                    const float2 a = __half22float2(sh[j]), m = __half22float2(mh[j]);
+                    const int k = c * 8 + 2 * j;
+                    v[i][2 * j] = (c < nchunk && k < valid) ? a.x + m.x : -INFINITY;
+                    v[i][2 * j + 1] = (c < nchunk && k + 1 < valid) ? a.y + m.y : -INFINITY;
+                    mx = fmaxf(mx, fmaxf(v[i][2 * j], v[i][2 * j + 1]));
+                }
             }
 #pragma unroll
-        for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
-        const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+            for (int m = 16; m > 0; m >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, m));
+            const float shift = (mx == -INFINITY) ? 0.f : mx * kLog2e;
+            float sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-            const int c = lane + 32 * i;
-            if (c < nchunk) {
-                uint4 o;
-                half2* oh = reinterpret_cast<half2*>(&o);
+            for (int i = 0; i < CH; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    oh[j] = __floats2half2_rn(v[i][2 * j] * inv, v[i][2 * j + 1] * inv);
-                sr[c] = o;
+                for (int j = 0; j < 8; ++j) {
+                    v[i][j] = exp2f(v[i][j] * kLog2e - shift);
+                    sum += v[i][j];
+                }
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, m);
+            const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+            if (row < nrow) {
+                uint4* sw = reinterpret_cast<uint4*>(scores + row * L);
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < nchunk) {
+                        uint4 o;
+                        half2* oh = reinterpret_cast<half2*>(&o);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            oh[j] = __floats2half2_rn(v[i][2 * j] * inv, v[i][2 * j + 1] * inv);
+                        __stcs(sw + c, o);
+                    }
+                }
             }
         }
     }
@@ -121,7 +138,7 @@ extern "C" int et_softmax_mask(void* scores, const void* mask, int nmat, int seq
     half* s = static_cast<half*>(scores);
     const half* m = static_cast<const half*>(mask);
     const long nrow = (long)nmat * seq_len;
-    long blocks = (nrow + 7) / 8;
+    long blocks = (nrow + 15) / 16;          // 8 warps per block, 2 rows per warp and iteration
     const long cap = (long)sm_count() * 8;
     if (blocks > cap) blocks = cap;
     const bool vec = seq_len % 8 == 0 && seq_len <= 2048 && aligned16(s) && (!m || aligned16(m));
