@@ -16,6 +16,7 @@ checkout under oracle/_ref/) on the same workload, composed in the reference's o
 absent it times the fp32 CPU oracle instead.
 """
 import argparse
+import collections
 import ctypes
 import json
 import os
@@ -134,14 +135,17 @@ def workload_config(args):
                   f"25 MB each) visited round-robin"}
 
 
-def timed(step, steps):
-    """`steps` calls of step(i) between two CUDA events on the current stream; returns ms per step."""
+def timed(step, steps, finish=None):
+    """`steps` calls of step(i) between two CUDA events on the current stream; returns ms per step.
+    `finish` (optional) runs before the closing event, e.g. to join collectives still in flight."""
     import torch
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(steps):
         step(i)
+    if finish:
+        finish()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / steps
@@ -263,7 +267,20 @@ def main():
     pk = peaks()
     orc = oracle_lib.load()
     lens = [SEQ] * BATCH
-    gathered = torch.zeros((world * T, D_MODEL), dtype=torch.float16, device="cuda") if world > 1 else None
+    # output shards are gathered with one NCCL all-gather per step, issued asynchronously: the next step's layer
+    # does not wait for it (ring of 4 destination buffers, at most 2 collectives in flight, all joined before the
+    # closing event of a timed region)
+    gathered = [torch.zeros((world * T, D_MODEL), dtype=torch.float16, device="cuda") for _ in range(4)] if world > 1 else None
+    pending = collections.deque()
+
+    def gather(i, out):
+        pending.append(dist.all_gather_into_tensor(gathered[i % 4], out, async_op=True))
+        if len(pending) > 2:
+            pending.popleft().wait()
+
+    def join():
+        while pending:
+            pending.popleft().wait()
 
     class Instance:
         """One independent copy of the workload: its own weights, input, output and scratch."""
@@ -284,16 +301,16 @@ def main():
             it = insts[i % len(insts)]
             it.enc.run_batch(it.out, it.x, lens, it.scratch)
             if world > 1:
-                dist.all_gather_into_tensor(gathered, it.out)
+                gather(i, it.out)
         return step
 
     def measure(insts, steps, warmup):
         step = layer_step(insts)
-        timed(step, 3 * len(insts))      # direct run, graph capture and first replay of every instance
-        timed(step, warmup)
+        timed(step, 3 * len(insts), join)   # direct run, graph capture and first replay of every instance
+        timed(step, warmup, join)
         if world > 1:
             dist.barrier()
-        ms = timed(step, steps)
+        ms = timed(step, steps, join)
         if world > 1:
             dist.barrier()
             t = torch.tensor([ms], dtype=torch.float64, device="cuda")
@@ -319,7 +336,7 @@ def main():
         it.x.copy_(hx[i % INSTANCES], non_blocking=True)
         it.enc.run_batch(it.out, it.x, lens, it.scratch)
         if world > 1:
-            dist.all_gather_into_tensor(gathered, it.out)
+            dist.all_gather_into_tensor(gathered[0], it.out)
         ho[i % INSTANCES].copy_(it.out, non_blocking=True)
         torch.cuda.synchronize()          # the caller needs the result on the host before its next batch
     for i in range(INSTANCES):

@@ -10,13 +10,19 @@
 
 namespace et {
 
-template <int CH>  // 16-byte chunks per lane; covers L <= CH*256
+// 2^x on the special-function unit; inputs here are <= 0 or -inf, results flush to zero below 2^-126.
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int CH, int R>  // CH 16-byte chunks per lane (L <= CH*256); R rows per warp and iteration
 __global__ void __launch_bounds__(256) softmax_mask_vec(half* __restrict__ scores,
                                                         const half* __restrict__ mask, long nrow,
                                                         int L, int valid) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int R = 2;   // rows per warp and iteration: twice the bytes in flight per warp
     const int lane = threadIdx.x & 31;
     const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long nwarp = ((long)gridDim.x * blockDim.x) >> 5;
@@ -67,7 +73,7 @@ __global__ void __launch_bounds__(256) softmax_mask_vec(half* __restrict__ score
             for (int i = 0; i < CH; ++i)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                    v[i][j] = exp2f(v[i][j] * kLog2e - shift);
+                    v[i][j] = ex2_fast(v[i][j] * kLog2e - shift);
                     sum += v[i][j];
                 }
 #pragma unroll
@@ -145,11 +151,11 @@ extern "C" int et_softmax_mask(void* scores, const void* mask, int nmat, int seq
     if (vec) {
         const int ch = (seq_len / 8 + 31) / 32;
         switch (ch) {
-            case 1: launch_pdl(softmax_mask_vec<1>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
-            case 2: launch_pdl(softmax_mask_vec<2>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
+            case 1: launch_pdl(softmax_mask_vec<1, 2>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
+            case 2: launch_pdl(softmax_mask_vec<2, 2>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
             case 3:
-            case 4: launch_pdl(softmax_mask_vec<4>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
-            default: launch_pdl(softmax_mask_vec<8>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
+            case 4: launch_pdl(softmax_mask_vec<4, 2>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
+            default: launch_pdl(softmax_mask_vec<8, 1>, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len); break;
         }
     } else {
         launch_pdl(softmax_mask_generic, dim3((unsigned)blocks), dim3(256), 0, st, s, m, nrow, seq_len, valid_len);
