@@ -64,3 +64,9 @@ extern "C" int et_debug_set_gemm_profile_buffer(void* dev_buf) {
     et::tile_gemm_set_profile_buffer(static_cast<long long*>(dev_buf));
     return ET_OK;
 }
+
+namespace et { void attention_tc_set_profile_buffer(long long* dev_buf); }
+extern "C" int et_debug_set_attention_profile_buffer(void* dev_buf) {
+    et::attention_tc_set_profile_buffer(static_cast<long long*>(dev_buf));
+    return ET_OK;
+}

@@ -18,6 +18,7 @@
 // Tensor path: warp-level mma.sync m16n8k16 with ldmatrix-fed fragments (flash-style online softmax,
 // P stays in registers). Widths per head up to 64 are supported (zero-padded in shared memory).
 #include <mutex>
+#include "attention.h"
 #include "common.h"
 
 namespace et {
@@ -391,7 +392,7 @@ int attention_launch(half* Z, const half* Q, const half* K, const half* V, const
                      int q_pitch, int v_pitch, const int* qk_head_ptr, const int* v_col_id,
                      const int* v_head_ptr, const half* mask, int mask_ld, const int* cu_seqlens,
                      const int* valid_lens, int batch, int uniform_len, int total_tokens, int d_model,
-                     int nhead, cudaStream_t st) {
+                     int nhead, cudaStream_t st, int max_len) {
     if (!Z || !V || (!scores && (!Q || !K))) return fail(ET_ERR_INVALID, "attention: null pointer");
     if (batch < 0 || nhead <= 0 || d_model <= 0 || d_model % nhead) return fail(ET_ERR_INVALID, "attention: bad dimensions");
     const int hd = d_model / nhead;
@@ -402,6 +403,13 @@ int attention_launch(half* Z, const half* Q, const half* K, const half* V, const
     if (!cu_seqlens && uniform_len <= 0 && batch > 0) return fail(ET_ERR_INVALID, "attention: no lengths given");
     if (batch == 0 || total_tokens == 0) return ET_OK;
     if (scores && cu_seqlens) return fail(ET_ERR_UNSUPPORTED, "attention: precomputed scores need equal-length sequences");
+    if (!scores && !qk_head_ptr && !v_head_ptr) {
+        // dense case: tensor-core (tcgen05) kernel when the shape is in its range
+        const int ml = cu_seqlens ? max_len : uniform_len;
+        const int rc = attention_tc_launch(Z, Q, K, V, q_pitch, v_pitch, mask, mask_ld, cu_seqlens, valid_lens, batch,
+                                           uniform_len, total_tokens, ml, d_model, nhead, st);
+        if (rc != ET_ERR_UNSUPPORTED) return rc;
+    }
     AttnParams p;
     p.Q = Q; p.K = K; p.V = V; p.Z = Z; p.mask = mask; p.scores = scores;
     p.q_pitch = q_pitch; p.v_pitch = v_pitch; p.z_pitch = d_model; p.mask_ld = mask_ld;

@@ -8,11 +8,17 @@ namespace et {
 // General form. Q/K share q_pitch; scores != null replaces Q K^T by precomputed, already scaled
 // scores [batch][nhead][L][L] (equal-length sequences only). cu_seqlens (device, batch+1 ints) or, when
 // null, `batch` sequences of uniform_len tokens each. valid_lens (device) limits the keys per sequence.
+// max_len: the longest sequence of the batch when the caller knows it (0 = unknown); it only selects the kernel.
 int attention_launch(half* Z, const half* Q, const half* K, const half* V, const half* scores,
                      int q_pitch, int v_pitch, const int* qk_head_ptr, const int* v_col_id,
                      const int* v_head_ptr, const half* mask, int mask_ld, const int* cu_seqlens,
                      const int* valid_lens, int batch, int uniform_len, int total_tokens, int d_model,
-                     int nhead, cudaStream_t st);
+                     int nhead, cudaStream_t st, int max_len = 0);
+// tcgen05 fast path (dense, head_dim 64, longest sequence known); ET_ERR_UNSUPPORTED outside its range.
+int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, int q_pitch, int v_pitch,
+                        const half* mask, int mask_ld, const int* cu_seqlens, const int* valid_lens, int batch,
+                        int uniform_len, int total_tokens, int max_len, int d_model, int nhead, cudaStream_t st);
+int attention_tc_error(int* code);
 int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, int d_model, int nhead,
                      cudaStream_t st);
 

@@ -1,0 +1,440 @@
+// On-the-fly attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA) for the dense case with
+// head_dim 64: the fast path behind et_attention_otf /
+// et_attention_batch (the mma.sync kernel in attention.cu covers every other variant).
+// Replaces kernels/attention.cu:51-134 of the reference for that case.
+//
+// A CTA owns 128 queries of one head of one sequence, one TMEM lane per query:
+//   S_j = Q K_j^T      SS UMMA 128x128x16 (x4), Q and the 128-key block K_j in shared memory (TMA, 128-byte
+//                      swizzle), fp32 S_j in 128 TMEM columns
+//   softmax            eight warps, two threads per query row (64 keys each): tcgen05.ld, scale (log2 domain),
+//                      additive mask, key validity, running max / sum in fp32, P_j = 2^(s - max) as packed fp16
+//                      into 64 more TMEM columns (tcgen05.st), O rescaled by 2^(old max - new max) in place
+//   O += P_j V_j       TS UMMA 128x64x16 (x8): A = P_j read from tensor memory, B = V_j in shared memory as loaded
+//                      (rows = keys), used as an MN-major operand
+//   epilogue           O / row sum -> fp16 -> global, rows beyond the sequence are not written
+// The S x S matrix never leaves the SM. K_j / V_j stream through a two-stage ring, so a CTA needs 80 KB of
+// shared memory and 256 TMEM columns and two CTAs share an SM: one CTA's softmax runs under the other's
+// UMMAs and loads. Every mbarrier wait is bounded; a wait that gives up
+// sets the error word and the CTA leaves through the common exit, freeing its tensor memory.
+#include "attention.h"
+#include "common.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace et {
+
+namespace {
+
+constexpr int kBQ = 128, kBK = 128, kHD = 64;
+constexpr int kTile = kBQ * kHD * 2;      // 16 KB: one 128 x 64 fp16 tile
+constexpr int kSoftmaxWarps = 8;          // two threads per query row, each owns 64 of the 128 keys of a block
+constexpr int kThreads = 32 * (kSoftmaxWarps + 1);   // + 1 warp whose lane 0 issues TMA and UMMA
+constexpr int kTmemCols = 256;            // S 128 | P 64 | O 64: two CTAs share an SM's tensor memory
+constexpr uint32_t kPCol = 128, kOCol = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct TcParams {
+    half* Z;
+    const half* mask;
+    const int* cu_seqlens;
+    const int* valid_lens;
+    int z_pitch, mask_ld, batch, uniform_len;
+    float scale_log2;
+    int* err;
+    long long* prof;   // ET_ATTN_PROFILE builds: clock64 stamps of CTA (0,0)
+};
+
+#ifdef ET_ATTN_PROFILE
+#define AT_STAMP(slot) do { if (p.prof && blockIdx.x == 0 && blockIdx.y == 0) p.prof[(slot)] = clock64(); } while (0)
+#else
+#define AT_STAMP(slot) do { } while (0)
+#endif
+
+struct TcShared {
+    uint64_t q_full, k_full[2], v_full[2];   // K/V blocks stream through a two-stage ring
+    uint64_t s_ready, p_ready, pv_done, o_done;
+    uint32_t tmem_base;
+    int seq[3];
+    volatile int abort;
+    float xmax[2][kBQ];   // block maximum of each half-row, exchanged between the two threads of a row
+    float xsum[2][kBQ];   // final row sums of each half
+};
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// The two warps that share a quarter of the rows (64 threads) meet on their own hardware barrier.
+__device__ __forceinline__ void named_pair_sync(int id) {
+    asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
+
+// 32 additive mask values of one query row (keys k0..k0+31), times log2(e); zero where there is no mask row.
+__device__ __forceinline__ void load_mask32(float (&mk)[32], const half* mrow, int k0, int limit, bool vec) {
+    if (!mrow) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mk[i] = 0.f;
+        return;
+    }
+    if (vec && k0 + 32 <= limit) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(mrow + k0) + c);
+            const half2* h2 = reinterpret_cast<const half2*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h2[i]);
+                mk[c * 8 + 2 * i] = f.x * kLog2e;
+                mk[c * 8 + 2 * i + 1] = f.y * kLog2e;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) mk[i] = (k0 + i < limit) ? __half2float(__ldg(mrow + k0 + i)) * kLog2e : 0.f;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
+                                                                  const __grid_constant__ CUtensorMap tmK,
+                                                                  const __grid_constant__ CUtensorMap tmV,
+                                                                  const __grid_constant__ TcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* sQ = smem;
+    uint8_t* sK = smem + kTile;          // 2 stages
+    uint8_t* sV = sK + 2 * kTile;        // 2 stages
+    TcShared* sh = reinterpret_cast<TcShared*>(sV + 2 * kTile);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y;
+    if (tid == 0) AT_STAMP(0);
+    pdl_launch_dependents();
+
+    if (tid == 0) {
+        mbar_init(&sh->q_full, 1);
+        for (int j = 0; j < 2; ++j) { mbar_init(&sh->k_full[j], 1); mbar_init(&sh->v_full[j], 1); }
+        mbar_init(&sh->s_ready, 1);
+        mbar_init(&sh->p_ready, 32 * kSoftmaxWarps);
+        mbar_init(&sh->pv_done, 1);
+        mbar_init(&sh->o_done, 1);
+        sh->abort = 0;
+        fence_mbar_init();
+    }
+    if (warp == kSoftmaxWarps) {
+        tmem_alloc(&sh->tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    pdl_wait();   // lengths and activations come from the preceding kernels
+    if (tid == 32) {
+        int b = -1, tok0 = 0, q0 = 0, blk = blockIdx.x;
+        if (p.cu_seqlens) {
+            for (int i = 0; i < p.batch; ++i) {
+                const int L = p.cu_seqlens[i + 1] - p.cu_seqlens[i];
+                const int nb = (L + kBQ - 1) / kBQ;
+                if (blk < nb) { b = i; tok0 = p.cu_seqlens[i]; q0 = blk * kBQ; break; }
+                blk -= nb;
+            }
+        } else {
+            const int nb = (p.uniform_len + kBQ - 1) / kBQ;
+            if (blk < nb * p.batch) { b = blk / nb; tok0 = b * p.uniform_len; q0 = (blk % nb) * kBQ; }
+        }
+        sh->seq[0] = b; sh->seq[1] = tok0; sh->seq[2] = q0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+    if (tid == 0) AT_STAMP(1);
+    const int b = sh->seq[0], tok0 = sh->seq[1], q0 = sh->seq[2];
+    int nkb = 0, L = 0, valid = 0;
+    if (b >= 0) {
+        L = p.cu_seqlens ? p.cu_seqlens[b + 1] - p.cu_seqlens[b] : p.uniform_len;
+        valid = p.valid_lens ? min(p.valid_lens[b], L) : L;
+        nkb = (valid + kBK - 1) / kBK;
+    }
+
+    if (b >= 0 && nkb > 0) {
+        if (warp == kSoftmaxWarps) {
+            if (lane == 0) {
+                auto load_kv = [&](int j) {
+                    const int st = j & 1;
+                    mbar_expect_tx(&sh->k_full[st], kTile);
+                    tma_load_2d(sK + (size_t)st * kTile, &tmK, h * kHD, tok0 + j * kBK, &sh->k_full[st]);
+                    mbar_expect_tx(&sh->v_full[st], kTile);
+                    tma_load_2d(sV + (size_t)st * kTile, &tmV, h * kHD, tok0 + j * kBK, &sh->v_full[st]);
+                };
+                mbar_expect_tx(&sh->q_full, kTile);
+                tma_load_2d(sQ, &tmQ, h * kHD, tok0 + q0, &sh->q_full);
+                load_kv(0);
+                if (nkb > 1) load_kv(1);
+                const uint32_t idesc_qk = make_idesc_f16(128, 128);
+                const uint32_t idesc_pv = make_idesc_f16(128, 64, false, true);   // V is an MN-major B operand
+                const uint32_t qa = smem_u32(sQ);
+                AT_STAMP(10);
+                bool ok = mbar_wait(&sh->q_full, 0);
+                AT_STAMP(11);
+                for (int j = 0; j < nkb && ok; ++j) {
+                    const int st = j & 1;
+                    const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+                    if (sh->abort) { ok = false; break; }
+                    // S = Q K_j^T (the S / P columns are free: P_{j-1} V_{j-1} has completed, see below)
+                    ok = mbar_wait(&sh->k_full[st], ph);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t ka = smem_u32(sK + (size_t)st * kTile);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks)
+                        umma_f16(tmem, make_smem_desc(qa + ks * 32, 16, 1024, 2), make_smem_desc(ka + ks * 32, 16, 1024, 2),
+                                 idesc_qk, ks > 0);
+                    umma_commit(&sh->s_ready);
+                    if (j == 0) AT_STAMP(13);
+                    // O += P_j V_j once the softmax warps have written P_j (and rescaled O)
+                    ok = mbar_wait(&sh->p_ready, (uint32_t)j & 1u) && mbar_wait(&sh->v_full[st], ph);
+                    if (!ok) break;
+                    AT_STAMP(14 + 2 * j);
+                    tc_fence_after();
+                    const uint32_t va = smem_u32(sV + (size_t)st * kTile);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        umma_f16_ts(tmem + kOCol, tmem + kPCol + ks * 8, make_smem_desc(va + ks * 2048, 0, 1024, 2), idesc_pv,
+                                    (j > 0 || ks > 0) ? 1u : 0u);
+                    umma_commit(&sh->pv_done);
+                    AT_STAMP(15 + 2 * j);
+                    if (j + 1 < nkb) {
+                        // the stage and the P columns are reused: wait until this block's UMMAs have finished
+                        ok = mbar_wait(&sh->pv_done, (uint32_t)j & 1u);
+                        if (!ok) break;
+                        if (j + 2 < nkb) load_kv(j + 2);
+                    }
+                }
+                umma_commit(&sh->o_done);
+                if (!ok) {
+                    atomicExch(p.err, 21);
+                    sh->abort = 1;
+                }
+            }
+        } else {
+            // ---- softmax warps: two threads per query row (TMEM lane), each owns 64 of a block's 128 keys
+            const int quarter = warp & 3, half_id = warp >> 2;
+            const int row = quarter * 32 + lane;
+            const int qr = q0 + row;                       // query index inside the sequence
+            const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+            const bool has_mask = p.mask != nullptr;   // uniform: the masked code path is separate from the plain one
+            const half* mrow = (has_mask && qr < L) ? p.mask + (size_t)qr * p.mask_ld : nullptr;
+            const bool mask_vec = has_mask && (p.mask_ld & 7) == 0 && (reinterpret_cast<uintptr_t>(p.mask) & 15) == 0;
+            const uint32_t s_addr = tmem + lane_base + (uint32_t)(half_id * 64);           // this thread's S columns
+            const uint32_t p_addr = tmem + lane_base + kPCol + (uint32_t)(half_id * 32);   // its packed P columns
+            const uint32_t o_addr = tmem + lane_base + kOCol + (uint32_t)(half_id * 32);   // the O columns it rescales/stores
+            float m_run = -INFINITY, l_run = 0.f;
+            bool ok = true;
+            for (int j = 0; j < nkb; ++j) {
+                int got = 1;
+                if (lane == 0) got = (!sh->abort && mbar_wait(&sh->s_ready, (uint32_t)j & 1u)) ? 1 : 0;
+                got = __shfl_sync(0xffffffffu, got, 0);
+                if (!got) {
+                    // keep the pair barriers balanced: the partner warp may still be inside the loop
+                    ok = false;
+                    sh->abort = 1;
+                    for (int jj = j; jj < nkb; ++jj) named_pair_sync(1 + quarter);
+                    break;
+                }
+                if (tid == 0) AT_STAMP(30 + 4 * j);
+                tc_fence_after();
+                const int k0 = j * kBK + half_id * 64;
+                // pass 1: maximum of the scaled, masked scores of this half-row, then of the whole row
+                float bmax = -INFINITY;
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(s_addr + c * 32, r);
+                    tmem_ld_wait();
+                    const int kc = k0 + c * 32;
+                    if (has_mask) {
+                        float mk[32];
+                        load_mask32(mk, mrow, kc, valid, mask_vec);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float v = fmaf(__uint_as_float(r[i]), p.scale_log2, mk[i]);
+                            bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float v = __uint_as_float(r[i]) * p.scale_log2;
+                            bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
+                        }
+                    }
+                }
+                sh->xmax[half_id][row] = bmax;
+                named_pair_sync(1 + quarter);
+                bmax = fmaxf(bmax, sh->xmax[half_id ^ 1][row]);
+                if (tid == 0) AT_STAMP(31 + 4 * j);
+                const float m_new = fmaxf(m_run, bmax);
+                const float shift = (m_new == -INFINITY) ? 0.f : m_new;
+                const float alpha = ex2_fast(m_run - shift);    // 0 when there was no previous block
+                // O accumulates in tensor memory; P_{j-1} V_{j-1} has completed (the issuer waited for it before
+                // it started this block's Q K^T). Each thread rescales its 32 of the 64 columns.
+                if (j > 0) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t r[16];
+                        tmem_ld16(o_addr + c * 16, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st16(o_addr + c * 16, r);
+                    }
+                }
+                if (tid == 0) AT_STAMP(32 + 4 * j);
+                // pass 2: P = 2^(s - max) as packed fp16 into the P columns
+                float bsum = 0.f;
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(s_addr + c * 32, r);
+                    tmem_ld_wait();
+                    const int kc = k0 + c * 32;
+                    float mk[32];
+                    if (has_mask) load_mask32(mk, mrow, kc, valid, mask_vec);
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float e[2];
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            float v = __uint_as_float(r[i + u]) * p.scale_log2 - shift;
+                            if (has_mask) v += mk[i + u];
+                            e[u] = (kc + i + u < valid) ? ex2_fast(v) : 0.f;
+                        }
+                        bsum += e[0] + e[1];
+                        pk[i >> 1] = pack2(e[0], e[1]);
+                    }
+                    tmem_st16(p_addr + c * 16, pk);
+                }
+                l_run = l_run * alpha + bsum;
+                m_run = m_new;
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&sh->p_ready);
+                if (tid == 0) AT_STAMP(33 + 4 * j);
+            }
+            // ---- epilogue: both halves' sums, then O / sum -> fp16 -> global
+            sh->xsum[half_id][row] = l_run;
+            int fin = 1;
+            if (lane == 0) fin = (ok && !sh->abort && mbar_wait(&sh->o_done, 0)) ? 1 : 0;
+            fin = __shfl_sync(0xffffffffu, fin, 0);
+            named_pair_sync(1 + quarter);
+            tc_fence_after();
+            if (tid == 0) AT_STAMP(50);
+            if (fin) {
+                const float l = l_run + sh->xsum[half_id ^ 1][row];
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                half* zrow = p.Z + (size_t)(tok0 + qr) * p.z_pitch + h * kHD + half_id * 32;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t r[16];
+                    tmem_ld16(o_addr + c * 16, r);
+                    tmem_ld_wait();
+                    if (qr < L) {
+                        uint4 o[2];
+                        uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            ow[i] = pack2(__uint_as_float(r[2 * i]) * inv, __uint_as_float(r[2 * i + 1]) * inv);
+                        *reinterpret_cast<uint4*>(zrow + c * 16) = o[0];
+                        *reinterpret_cast<uint4*>(zrow + c * 16 + 8) = o[1];
+                    }
+                }
+            } else if (lane == 0 && !sh->abort) {
+                atomicExch(p.err, 22);
+                sh->abort = 1;
+            }
+        }
+    } else if (b >= 0 && warp < 4) {
+        // no valid key: the output rows are zero
+        const int qr = q0 + warp * 32 + lane;
+        if (qr < L) {
+            uint4* z = reinterpret_cast<uint4*>(p.Z + (size_t)(tok0 + qr) * p.z_pitch + h * kHD);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) z[i] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (tid == 0) AT_STAMP(51);
+    if (warp == kSoftmaxWarps) tmem_dealloc(tmem, kTmemCols);
+}
+
+long long* g_attn_prof = nullptr;
+
+int* g_tc_err = nullptr;   // device error word shared by all launches of this process, one per device would be
+int g_tc_err_dev = -1;     // better; the kernels only ever write non-zero on a timed-out wait
+
+}  // namespace
+
+// Fast path. Returns ET_ERR_UNSUPPORTED (without touching anything) when the case is outside its range, so the
+// caller can use the general kernel instead.
+int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, int q_pitch, int v_pitch,
+                        const half* mask, int mask_ld, const int* cu_seqlens, const int* valid_lens, int batch,
+                        int uniform_len, int total_tokens, int max_len, int d_model, int nhead, cudaStream_t st) {
+    if (d_model / nhead != kHD || d_model % nhead) return ET_ERR_UNSUPPORTED;
+    if (max_len <= 0) return ET_ERR_UNSUPPORTED;   // longest sequence unknown: the caller uses the general kernel
+    if ((q_pitch & 7) || (v_pitch & 7) || (d_model & 7) || !aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(Z))
+        return ET_ERR_UNSUPPORTED;
+    if (batch <= 0 || total_tokens <= 0) return ET_OK;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!g_tc_err || g_tc_err_dev != dev) {
+        if (cudaMalloc(&g_tc_err, sizeof(int)) != cudaSuccess) return fail(ET_ERR_CUDA, "attention: cudaMalloc failed");
+        cudaMemset(g_tc_err, 0, sizeof(int));
+        g_tc_err_dev = dev;
+    }
+    CUtensorMap tq, tk, tv;
+    const uint64_t rows = (uint64_t)total_tokens;
+    // the column extent covers all heads of the operand; Q/K/V may be slices of one fused [tokens x 3 d_model] buffer
+    if (!make_tmap_2d_f16(&tq, Q, rows, (uint64_t)d_model, (uint64_t)q_pitch, kBQ, kHD, true) ||
+        !make_tmap_2d_f16(&tk, K, rows, (uint64_t)d_model, (uint64_t)q_pitch, kBK, kHD, true) ||
+        !make_tmap_2d_f16(&tv, V, rows, (uint64_t)d_model, (uint64_t)v_pitch, kBK, kHD, true))
+        return fail(ET_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed");
+    TcParams p;
+    p.Z = Z; p.mask = mask; p.cu_seqlens = cu_seqlens; p.valid_lens = valid_lens;
+    p.z_pitch = d_model; p.mask_ld = mask_ld; p.batch = batch; p.uniform_len = uniform_len;
+    p.scale_log2 = kLog2e / sqrtf((float)kHD);
+    p.err = g_tc_err;
+    p.prof = g_attn_prof;
+    const size_t smem = (size_t)kTile * 5 + sizeof(TcShared) + 1024;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        if (e != cudaSuccess) return cuda_status(e, "attention: shared memory opt-in");
+        attr_done = true;
+    }
+    const int nblk = cu_seqlens ? (total_tokens + kBQ - 1) / kBQ + batch : batch * ((uniform_len + kBQ - 1) / kBQ);
+    return cuda_status(launch_pdl(attention_tc_kernel, dim3(nblk, nhead), dim3(kThreads), smem, st, tq, tk, tv, p),
+                       "attention (tcgen05) launch");
+}
+
+void attention_tc_set_profile_buffer(long long* dev_buf) { g_attn_prof = dev_buf; }
+
+// Reads and clears the error word of the tcgen05 attention kernel (synchronises). 0 = no wait gave up.
+int attention_tc_error(int* code) {
+    *code = 0;
+    if (!g_tc_err) return ET_OK;
+    cudaError_t e = cudaMemcpy(code, g_tc_err, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_status(e, "attention error read");
+    if (*code) cudaMemset(g_tc_err, 0, sizeof(int));
+    return ET_OK;
+}
+
+}  // namespace et

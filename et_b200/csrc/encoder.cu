@@ -183,7 +183,7 @@ static int encoder_common(Encoder* e, int d_model, int seq_len, int nheads, half
 // [0] Q then the attention-output projection / first LayerNorm result, [1] K, [2] V, [3] attention output,
 // [1..4] the T x d_ff hidden activations; scores (materialised variant) follow at 5*T*d_model.
 static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch, int T, const int* cu_seqlens,
-                           const int* valid_lens, int batch, int uniform_len, cudaStream_t st) {
+                           const int* valid_lens, int batch, int uniform_len, cudaStream_t st, int max_len = 0) {
     const size_t td = (size_t)T * e->d_model;
     half* b0 = scratch; half* b1 = scratch + td; half* b2 = scratch + 2 * td; half* b3 = scratch + 3 * td;
     int rc;
@@ -217,7 +217,7 @@ static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch,
         scores = sbuf;
     }
     if ((rc = attention_launch(b3, b0, b1, b2, scores, q_pitch, v_pitch, qk_hp, v_id, v_hp, e->d_mask, e->seq_len,
-                               cu_seqlens, valid_lens, batch, uniform_len, T, e->d_model, e->nheads, st)))
+                               cu_seqlens, valid_lens, batch, uniform_len, T, e->d_model, e->nheads, st, max_len)))
         return rc;
     b1 = scratch + td;
     if ((rc = tile_linear_run(e->lin[3], b0, b3, T, 0, st))) return rc;
@@ -323,11 +323,12 @@ int et_attention_static_scores(void* out, const void* Q, const void* K, const vo
 int et_attention_batch(void* out, const void* Q, const void* K, const void* V, int qk_pitch, int v_pitch,
                        const int* qk_head_ptr, const int* v_col_id, const int* v_head_ptr, const void* mask,
                        int mask_ld, const int* cu_seqlens, const int* valid_lens, int batch, int uniform_len,
-                       int total_tokens, int d_model, int nhead, void* stream) {
+                       int max_seq_len, int total_tokens, int d_model, int nhead, void* stream) {
     return et::attention_launch(static_cast<half*>(out), static_cast<const half*>(Q), static_cast<const half*>(K),
                                 static_cast<const half*>(V), nullptr, qk_pitch, v_pitch, qk_head_ptr, v_col_id,
                                 v_head_ptr, static_cast<const half*>(mask), mask_ld, cu_seqlens, valid_lens, batch,
-                                uniform_len, total_tokens, d_model, nhead, static_cast<cudaStream_t>(stream));
+                                uniform_len, total_tokens, d_model, nhead, static_cast<cudaStream_t>(stream),
+                                max_seq_len);
 }
 
 // ------------------------------------------------------------------------------ encoders
@@ -499,7 +500,7 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (!e->use_graphs || cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
         return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
-                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st, max_len);
     std::vector<int64_t> key = {(int64_t)(intptr_t)out, (int64_t)(intptr_t)in, (int64_t)(intptr_t)scratch,
                                 (int64_t)batch, (int64_t)(valid_lens_host != nullptr), (int64_t)e->materialize_scores};
     for (int v : meta) key.push_back(v);
@@ -517,15 +518,15 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
     if (slot->exec) return et::cuda_status(cudaGraphLaunch(slot->exec, st), "et_encoder_run_batch: graph launch");
     if (slot->seen++ == 0)
         return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
-                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st, max_len);
     if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
         cudaGetLastError();
         return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
-                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st, max_len);
     }
     const int frc = et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
                                         static_cast<half*>(scratch), T, cu, vl, batch,
-                                        uniform ? seq_lens_host[0] : 0, st);
+                                        uniform ? seq_lens_host[0] : 0, st, max_len);
     cudaGraph_t graph = nullptr;
     const cudaError_t ce = cudaStreamEndCapture(st, &graph);
     if (frc != ET_OK || ce != cudaSuccess || !graph) {
@@ -533,7 +534,7 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
         cudaGetLastError();
         e->use_graphs = false;   // fall back to plain launches for this encoder
         return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
-                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st, max_len);
     }
     const cudaError_t ie = cudaGraphInstantiate(&slot->exec, graph, 0);
     cudaGraphDestroy(graph);
@@ -542,7 +543,7 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
         cudaGetLastError();
         e->use_graphs = false;
         return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
-                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st);
+                                   static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st, max_len);
     }
     return et::cuda_status(cudaGraphLaunch(slot->exec, st), "et_encoder_run_batch: graph launch");
 }

@@ -162,14 +162,14 @@ def attention_static_scores(out, Q, K, V, mask, seq_len, d_model, nhead, stream=
 
 
 def attention_batch(out, Q, K, V, d_model, nhead, cu_seqlens=None, valid_lens=None, batch=1, uniform_len=0,
-                    total_tokens=None, mask=None, mask_ld=0, qk_pitch=None, v_pitch=None, qk_head_ptr=None,
+                    max_seq_len=0, total_tokens=None, mask=None, mask_ld=0, qk_pitch=None, v_pitch=None, qk_head_ptr=None,
                     v_col_id=None, v_head_ptr=None, stream=None):
     total = Q.shape[0] if total_tokens is None else total_tokens
     check(lib().et_attention_batch(ptr(out), ptr(Q), ptr(K), ptr(V),
                                    _i(Q.shape[1] if qk_pitch is None else qk_pitch),
                                    _i(V.shape[1] if v_pitch is None else v_pitch), ptr(qk_head_ptr),
                                    ptr(v_col_id), ptr(v_head_ptr), ptr(mask), _i(mask_ld), ptr(cu_seqlens),
-                                   ptr(valid_lens), _i(batch), _i(uniform_len), _i(total), _i(d_model),
+                                   ptr(valid_lens), _i(batch), _i(uniform_len), _i(max_seq_len), _i(total), _i(d_model),
                                    _i(nhead), stream_ptr(stream)))
     return out
 

@@ -127,11 +127,13 @@ int et_attention_static_scores(void* out, const void* Q, const void* K, const vo
  * sequences are packed back to back; cu_seqlens (device, batch+1 ints) gives their token offsets, or NULL
  * for `batch` sequences of uniform_len tokens. valid_lens (device, may be NULL) excludes keys at or beyond
  * valid_lens[b] (key padding). Q and K share qk_pitch; qk_head_ptr / v_head_ptr + v_col_id (device, may be
- * NULL) select compact per-head column windows as in et_attention_prune. */
+ * NULL) select compact per-head column windows as in et_attention_prune. max_seq_len: the longest sequence
+ * when cu_seqlens is given (0 = unknown); it only selects between the tensor-core kernel for dense heads of
+ * 64 with at most 512 keys and the general kernel. */
 int et_attention_batch(void* out, const void* Q, const void* K, const void* V, int qk_pitch, int v_pitch,
                        const int* qk_head_ptr, const int* v_col_id, const int* v_head_ptr, const void* mask,
                        int mask_ld, const int* cu_seqlens, const int* valid_lens, int batch, int uniform_len,
-                       int total_tokens, int d_model, int nhead, void* stream);
+                       int max_seq_len, int total_tokens, int d_model, int nhead, void* stream);
 
 /* ---- pruned-format generators (host) ----------------------------------------------------------
  * Seeded and reproducible. bernoulli == 0 keeps exactly floor(total*(1-sparsity)) tiles (a block-row's

@@ -98,9 +98,14 @@ def test_attention_batch_varlen(et, orc, lens):
     want = orc.attention(Q, K, V, lens, d, H)
     cu = dev(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32))
     out = torch.full((T, d), float("nan"), dtype=torch.float16, device="cuda")
-    et.attention_batch(out, dev(Q), dev(K), dev(V), d, H, cu_seqlens=cu, batch=len(lens), total_tokens=T)
+    et.attention_batch(out, dev(Q), dev(K), dev(V), d, H, cu_seqlens=cu, batch=len(lens), total_tokens=T,
+                       max_seq_len=max(lens))          # tensor-core kernel (all lengths <= 512)
     torch.cuda.synchronize()
     util.assert_close(host(out), want, what=f"varlen attention {lens}")
+    out2 = torch.full((T, d), float("nan"), dtype=torch.float16, device="cuda")
+    et.attention_batch(out2, dev(Q), dev(K), dev(V), d, H, cu_seqlens=cu, batch=len(lens), total_tokens=T)
+    torch.cuda.synchronize()                           # longest length not given: general kernel
+    util.assert_close(host(out2), want, what=f"varlen attention, general kernel {lens}")
 
 
 def test_attention_batch_key_padding_equals_unpadded(et, orc):
@@ -115,7 +120,8 @@ def test_attention_batch_key_padding_equals_unpadded(et, orc):
     rows = np.concatenate([np.arange(b * S, b * S + lens[b]) for b in range(B)])
     cu = dev(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32))
     out_var = torch.zeros((len(rows), d), dtype=torch.float16, device="cuda")
-    et.attention_batch(out_var, dev(Q[rows]), dev(K[rows]), dev(V[rows]), d, H, cu_seqlens=cu, batch=B)
+    et.attention_batch(out_var, dev(Q[rows]), dev(K[rows]), dev(V[rows]), d, H, cu_seqlens=cu, batch=B,
+                       max_seq_len=max(lens))
     torch.cuda.synchronize()
     assert torch.equal(out_pad[torch.from_numpy(rows).cuda()], out_var)
     want = orc.attention(Q, K, V, [S] * B, d, H, valid_lens=lens)
