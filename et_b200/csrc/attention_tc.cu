@@ -29,8 +29,8 @@ constexpr int kBQ = 128, kBK = 128, kHD = 64;
 constexpr int kTile = kBQ * kHD * 2;      // 16 KB: one 128 x 64 fp16 tile
 constexpr int kSoftmaxWarps = 8;          // two threads per query row, each owns 64 of the 128 keys of a block
 constexpr int kThreads = 32 * (kSoftmaxWarps + 1);   // + 1 warp whose lane 0 issues TMA and UMMA
-constexpr int kTmemCols = 256;            // S 128 | P 64 | O 64: two CTAs share an SM's tensor memory
-constexpr uint32_t kPCol = 128, kOCol = 192;
+constexpr int kTmemCols = 256;            // S/P 128 | O 64 | row sums 16: two CTAs share an SM's tensor memory
+constexpr uint32_t kOCol = 128, kSumCol = 192;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct TcParams {
@@ -57,7 +57,7 @@ struct TcShared {
     int seq[3];
     volatile int abort;
     float xmax[2][kBQ];   // block maximum of each half-row, exchanged between the two threads of a row
-    float xsum[2][kBQ];   // final row sums of each half
+    __align__(16) half ones[256];   // a 16 x 16 B operand of ones: P . ones^T puts the row sums of P in 16 TMEM columns
 };
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -70,6 +70,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
 __device__ __forceinline__ float ex2_fast(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// 2^x for two fp16 values at once (one special-function op); P is stored in fp16 anyway.
+__device__ __forceinline__ uint32_t ex2_h2(uint32_t x) {
+    uint32_t y;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
     return y;
 }
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -132,6 +138,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
         sh->abort = 0;
         fence_mbar_init();
     }
+    if (tid < 128) reinterpret_cast<uint32_t*>(sh->ones)[tid] = 0x3c003c00u;   // 1.0 | 1.0
+    fence_proxy_async_smem();
     if (warp == kSoftmaxWarps) {
         tmem_alloc(&sh->tmem_base, kTmemCols);
         tmem_relinquish();
@@ -181,6 +189,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                 if (nkb > 1) load_kv(1);
                 const uint32_t idesc_qk = make_idesc_f16(128, 128);
                 const uint32_t idesc_pv = make_idesc_f16(128, 64, false, true);   // V is an MN-major B operand
+                const uint32_t idesc_sum = make_idesc_f16(128, 16);
+                const uint64_t ones_desc = make_smem_desc(smem_u32(sh->ones), 128, 256, 0);
                 const uint32_t qa = smem_u32(sQ);
                 AT_STAMP(10);
                 bool ok = mbar_wait(&sh->q_full, 0);
@@ -207,9 +217,13 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                     tc_fence_after();
                     const uint32_t va = smem_u32(sV + (size_t)st * kTile);
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        umma_f16_ts(tmem + kOCol, tmem + kPCol + ks * 8, make_smem_desc(va + ks * 2048, 0, 1024, 2), idesc_pv,
-                                    (j > 0 || ks > 0) ? 1u : 0u);
+                    for (int ks = 0; ks < 8; ++ks) {
+                        // P of keys 16ks..16ks+15: each half-row's P sits at the start of its own half of the S columns
+                        const uint32_t pa = tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8);
+                        const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u;
+                        umma_f16_ts(tmem + kOCol, pa, make_smem_desc(va + ks * 2048, 0, 1024, 2), idesc_pv, acc);
+                        umma_f16_ts(tmem + kSumCol, pa, ones_desc, idesc_sum, acc);
+                    }
                     umma_commit(&sh->pv_done);
                     AT_STAMP(15 + 2 * j);
                     if (j + 1 < nkb) {
@@ -235,9 +249,10 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
             const half* mrow = (has_mask && qr < L) ? p.mask + (size_t)qr * p.mask_ld : nullptr;
             const bool mask_vec = has_mask && (p.mask_ld & 7) == 0 && (reinterpret_cast<uintptr_t>(p.mask) & 15) == 0;
             const uint32_t s_addr = tmem + lane_base + (uint32_t)(half_id * 64);           // this thread's S columns
-            const uint32_t p_addr = tmem + lane_base + kPCol + (uint32_t)(half_id * 32);   // its packed P columns
+            const uint32_t p_addr = s_addr;   // its packed P goes over the S columns it has already consumed
             const uint32_t o_addr = tmem + lane_base + kOCol + (uint32_t)(half_id * 32);   // the O columns it rescales/stores
-            float m_run = -INFINITY, l_run = 0.f;
+            const uint32_t sum_addr = tmem + lane_base + kSumCol;
+            float m_run = -INFINITY;
             bool ok = true;
             for (int j = 0; j < nkb; ++j) {
                 int got = 1;
@@ -255,6 +270,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                 const int k0 = j * kBK + half_id * 64;
                 // pass 1: maximum of the scaled, masked scores of this half-row, then of the whole row
                 float bmax = -INFINITY;
+                const bool all_valid = k0 + 64 <= valid;   // uniform per warp: no per-key validity selects needed
                 for (int c = 0; c < 2; ++c) {
                     uint32_t r[32];
                     tmem_ld32(s_addr + c * 32, r);
@@ -268,6 +284,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                             const float v = fmaf(__uint_as_float(r[i]), p.scale_log2, mk[i]);
                             bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
                         }
+                    } else if (all_valid) {
+                        float raw = -INFINITY;   // the scale is positive: scale the maximum once
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) raw = fmaxf(raw, __uint_as_float(r[i]));
+                        bmax = fmaxf(bmax, raw * p.scale_log2);
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
@@ -295,49 +316,67 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                         for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
                         tmem_st16(o_addr + c * 16, r);
                     }
+                    if (half_id == 0) {   // the row sums accumulate next to O and are rescaled with it
+                        uint32_t r[16];
+                        tmem_ld16(sum_addr, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st16(sum_addr, r);
+                    }
                 }
                 if (tid == 0) AT_STAMP(32 + 4 * j);
                 // pass 2: P = 2^(s - max) as packed fp16 into the P columns
-                float bsum = 0.f;
+                const float nshift = -shift;
                 for (int c = 0; c < 2; ++c) {
                     uint32_t r[32];
                     tmem_ld32(s_addr + c * 32, r);
                     tmem_ld_wait();
                     const int kc = k0 + c * 32;
-                    float mk[32];
-                    if (has_mask) load_mask32(mk, mrow, kc, valid, mask_vec);
                     uint32_t pk[16];
+                    if (has_mask) {
+                        float mk[32];
+                        load_mask32(mk, mrow, kc, valid, mask_vec);
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float e[2];
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-                            float v = __uint_as_float(r[i + u]) * p.scale_log2 - shift;
-                            if (has_mask) v += mk[i + u];
-                            e[u] = (kc + i + u < valid) ? ex2_fast(v) : 0.f;
+                        for (int i = 0; i < 32; i += 2) {
+                            float a = fmaf(__uint_as_float(r[i]), p.scale_log2, nshift) + mk[i];
+                            float bq = fmaf(__uint_as_float(r[i + 1]), p.scale_log2, nshift) + mk[i + 1];
+                            a = (kc + i < valid) ? a : -INFINITY;
+                            bq = (kc + i + 1 < valid) ? bq : -INFINITY;
+                            pk[i >> 1] = ex2_h2(pack2(a, bq));
                         }
-                        bsum += e[0] + e[1];
-                        pk[i >> 1] = pack2(e[0], e[1]);
+                    } else if (all_valid) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r[i]), p.scale_log2, nshift),
+                                                      fmaf(__uint_as_float(r[i + 1]), p.scale_log2, nshift)));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            const float a = (kc + i < valid) ? fmaf(__uint_as_float(r[i]), p.scale_log2, nshift) : -INFINITY;
+                            const float bq = (kc + i + 1 < valid) ? fmaf(__uint_as_float(r[i + 1]), p.scale_log2, nshift) : -INFINITY;
+                            pk[i >> 1] = ex2_h2(pack2(a, bq));
+                        }
                     }
                     tmem_st16(p_addr + c * 16, pk);
                 }
-                l_run = l_run * alpha + bsum;
                 m_run = m_new;
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(&sh->p_ready);
                 if (tid == 0) AT_STAMP(33 + 4 * j);
             }
-            // ---- epilogue: both halves' sums, then O / sum -> fp16 -> global
-            sh->xsum[half_id][row] = l_run;
+            // ---- epilogue: O / row sum -> fp16 -> global
             int fin = 1;
             if (lane == 0) fin = (ok && !sh->abort && mbar_wait(&sh->o_done, 0)) ? 1 : 0;
             fin = __shfl_sync(0xffffffffu, fin, 0);
-            named_pair_sync(1 + quarter);
             tc_fence_after();
             if (tid == 0) AT_STAMP(50);
             if (fin) {
-                const float l = l_run + sh->xsum[half_id ^ 1][row];
+                uint32_t sr[16];
+                tmem_ld16(sum_addr, sr);
+                tmem_ld_wait();
+                const float l = __uint_as_float(sr[0]);
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 half* zrow = p.Z + (size_t)(tok0 + qr) * p.z_pitch + h * kHD + half_id * 32;
 #pragma unroll

@@ -44,7 +44,7 @@ constexpr int kPanel = 64;          // columns per panel
 constexpr int kSlices = kKC / 16;   // UMMA K steps per chunk
 constexpr int kMaxNB = 24;          // block-rows per CTA (384 accumulator columns)
 constexpr int kSlotCols = kKC / 2;  // TMEM columns of one A slot
-constexpr int kMaxSlots = 6;
+constexpr int kMaxSlots = 4;
 constexpr int kIssuers = 8;         // UMMA-issuing warps
 constexpr int kMovers = 2;          // tcgen05.cp-issuing warps, alternating chunks
 constexpr int kFirstIssuer = 1 + kMovers;
@@ -61,7 +61,7 @@ struct GemmParams {
     const uint8_t* stream;   // packed blocks
     half* Y;
     const half* bias;
-    int T, N, k_chunks, nb, stage_b_bytes, slots, gelu;
+    int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, slots, a_slots, panel_bufs, gelu;
     int* err;
     uint2 first[kDirInParams];   // dir[chunk][0] for chunk < kDirInParams: no global load before the first TMA
     long long* prof;         // optional per-role clock64 stamps of CTA (0,0) (ET_GEMM_PROFILE builds only)
@@ -106,14 +106,15 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 }
 
 struct Shared {
-    uint64_t full[kMaxSlots];       // slot filled: two activation panels + the weight block (TMA)
-    uint64_t a_ready[kMaxSlots];    // the slot's activations are in tensor memory (mover commit)
-    uint64_t slot_free[kMaxSlots];  // every issuer's UMMAs on the slot have completed (8 commits)
-    uint64_t acc_done;              // 8 issuer commits after the last chunk
+    uint64_t full[kMaxSlots];       // stage filled: two activation panels + the weight block (TMA)
+    uint64_t a_ready[kMaxSlots];    // the chunk's activations are in their tensor-memory slot (mover commit)
+    uint64_t slot_free[kMaxSlots];  // every issuer's UMMAs on the stage have completed (8 commits)
+    uint64_t acc_done;              // 8 issuer commits after a tile's last chunk
     uint32_t tmem_base;
-    volatile int abort;
-    uint2 dir[kMaxKChunks];                // this CTA's row of the block directory
-    __align__(16) half bias[kMaxNB * 16];  // this chunk's bias
+    volatile int abort;         // any role gave up: everybody winds down
+    volatile int issuer_abort;  // written by issuer warps only, before a tile's last named barrier, and read
+                                // after it: all eight warps leave the tile loop at the same tile
+    __align__(16) half bias[kMaxNB * 16];  // the current tile's bias
 };
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
@@ -122,113 +123,91 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 __device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+__device__ __forceinline__ void tma_store_wait_read_1() {
+    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 
+// Persistent: CTA c processes tiles c, c + gridDim.x, ... (tile = slab * n_chunks + chunk, so CTAs that run
+// together share activations in L2). The slot ring runs on across tiles: while the issuer warps convert and
+// store one tile, the producer and the movers already stage the first chunks of the next.
 __global__ void __launch_bounds__(kThreads, 1)
 tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int slot_bytes = kXStageBytes + p.stage_b_bytes;   // multiple of 1024
-    const int ring_bytes = max(p.slots * slot_bytes, ((p.nb + 3) / 4) * kPanelBytes);
-    Shared* sh = reinterpret_cast<Shared*>(smem + ring_bytes);
+    uint8_t* panels = smem + (size_t)p.slots * slot_bytes;   // one or two 16 KB output panels
+    Shared* sh = reinterpret_cast<Shared*>(panels + p.panel_bufs * kPanelBytes);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int slab = blockIdx.x, chunk = blockIdx.y;
-    const int R = p.slots;
-    const uint32_t a_col0 = 512u - (uint32_t)(R * kSlotCols);
+    // Two rings with one chunk counter: R shared-memory stages (activations + weight block; a stage is free
+    // once the chunk's UMMAs have completed, because they read the weights from it) and RA <= R tensor-memory
+    // slots for the A operand. A chunk's tensor-memory slot is free when the chunk RA before it is done, which
+    // the movers read from the same slot_free barriers with a lag.
+    const int R = p.slots, RA = p.a_slots;
+    const int G = gridDim.x;
+    const uint32_t a_col0 = 512u - (uint32_t)(RA * kSlotCols);
+    const int my_tiles = (p.n_tiles - (int)blockIdx.x + G - 1) / G;
     if (tid == 0) ET_STAMP(0);
     pdl_launch_dependents();   // the next kernel may set itself up on idle SMs while this one runs
 
     if (warp == 0) {
-        // ---------------- producer warp: starts at once; the other warps set up tensor memory meanwhile.
-        // Lane 0 issues the copies, lane 1 polls slot_free (a wait by the thread that has just issued a
-        // bulk copy costs several hundred clocks), lanes 2.. fetch this CTA's row of the directory.
+        // ---------------- producer warp: lane 0 issues the copies, lane 1 polls slot_free (a wait by the thread
+        // that has just issued a bulk copy costs several hundred clocks)
         {
-            const int nbar = 3 * R + 1;   // one barrier per lane
-            if (lane < nbar) {
-                if (lane < R) mbar_init(&sh->full[lane], 1);
-                else if (lane < 2 * R) mbar_init(&sh->a_ready[lane - R], 1);
-                else if (lane < 3 * R) mbar_init(&sh->slot_free[lane - 2 * R], kIssuers);
-                else mbar_init(&sh->acc_done, kIssuers);
-                fence_mbar_init();
+            // one barrier per lane
+            if (lane < kMaxSlots) mbar_init(&sh->full[lane], 1);
+            else if (lane < 2 * kMaxSlots) mbar_init(&sh->a_ready[lane - kMaxSlots], 1);
+            else if (lane < 3 * kMaxSlots) mbar_init(&sh->slot_free[lane - 2 * kMaxSlots], kIssuers);
+            else if (lane == 3 * kMaxSlots) mbar_init(&sh->acc_done, kIssuers);
+            if (lane <= 3 * kMaxSlots) fence_mbar_init();
+            if (lane == 0) {
+                sh->abort = 0;
+                sh->issuer_abort = 0;
             }
-            if (lane == 0) sh->abort = 0;
         }
         __syncwarp();
         named_barrier_arrive(2, kThreads);   // barriers are initialised: release the other warps
         if (lane == 0) ET_STAMP(8);
-        // Everything above touched only this kernel's own resources and constant weights. The activations may
-        // still be in the making: wait for the preceding kernels before the first copy (lane 0 issues them all).
+        // Everything above touched only this kernel's own resources. The activations may still be in the making:
+        // wait for the preceding kernels before the first copy (lane 0 issues them all).
         if (lane == 0) pdl_wait();
-        // directory loads are issued now and only consumed at the rendezvous below, so nobody waits on them here
-        const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
-        uint2 pre[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int i = lane - 2 + 30 * j;
-            pre[j] = (lane >= 2 && i < p.k_chunks) ? __ldg(gdir + i) : make_uint2(0, 0);
-        }
         int issued = 0, r = 0;
         uint32_t ph = 0;
-        bool dir_ready = false;   // warp-level rendezvous with the lanes that loaded the directory
         bool alive = true;
-        for (int kc = 0; kc < p.k_chunks && alive; ++kc) {
-            int go = 1;
-            if (lane == 1) go = (!sh->abort && mbar_wait(&sh->slot_free[r], ph ^ 1u)) ? 1 : 0;
-            go = __shfl_sync(0xffffffffu, go, 1);
-            if (lane == 0) ET_STAMP(900 + kc);
-            if (!go) {
-                if (lane == 0 && !sh->abort) {
-                    atomicExch(p.err, 11);
-                    sh->abort = 1;
-                }
-                alive = false;
-                break;
-            }
-            const bool need_dir = !(kc == 0 && chunk < kDirInParams);
-            if (need_dir && !dir_ready) {
-                // the activation copy does not need the directory: it goes out before the rendezvous
-                if (lane == 0) {
-                    mbar_expect_tx_only(&sh->full[r], kXStageBytes);
-                    tma_load_3d(smem + (size_t)r * slot_bytes, &tmX, 0, slab * kSlab, kc * (kKC / kPanel), &sh->full[r]);
-                }
-                if (lane >= 2) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int i = lane - 2 + 30 * j;
-                        if (i < p.k_chunks) sh->dir[i] = pre[j];
+        for (int tl = 0; tl < my_tiles && alive; ++tl) {
+            const int tile = (int)blockIdx.x + tl * G;
+            const int slab = tile / p.n_chunks, chunk = tile - slab * p.n_chunks;
+            const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
+            // directory entries: the first one of the first tile comes from the kernel parameters, the others are
+            // fetched one chunk ahead
+            uint2 dnext = (tl == 0 && chunk < kDirInParams) ? p.first[chunk] : (lane == 0 ? __ldg(gdir) : make_uint2(0, 0));
+            for (int kc = 0; kc < p.k_chunks; ++kc) {
+                const uint2 d = dnext;
+                if (lane == 0 && kc + 1 < p.k_chunks) dnext = __ldg(gdir + kc + 1);
+                int go = 1;
+                if (lane == 1) go = (!sh->abort && mbar_wait(&sh->slot_free[r], ph ^ 1u)) ? 1 : 0;
+                go = __shfl_sync(0xffffffffu, go, 1);
+                if (lane == 0 && issued < 64) ET_STAMP(900 + issued);
+                if (!go) {
+                    if (lane == 0 && !sh->abort) {
+                        atomicExch(p.err, 11);
+                        sh->abort = 1;
                     }
-                    for (int i = lane - 2 + 120; i < p.k_chunks; i += 30) sh->dir[i] = __ldg(gdir + i);
+                    alive = false;
+                    break;
                 }
-                __syncwarp();
-                dir_ready = true;
                 if (lane == 0) {
-                    const uint2 d = sh->dir[kc];
-                    mbar_expect_tx(&sh->full[r], d.y * 16u);
-                    bulk_load(smem + (size_t)r * slot_bytes + kXStageBytes, p.stream + (size_t)d.x * 16u, d.y * 16u,
-                              &sh->full[r]);
-                    ET_STAMP(100 + kc);
+                    uint8_t* st = smem + (size_t)r * slot_bytes;
+                    const uint32_t bbytes = d.y * 16u;
+                    mbar_expect_tx(&sh->full[r], kXStageBytes + bbytes);
+                    tma_load_3d(st, &tmX, 0, slab * kSlab, kc * (kKC / kPanel), &sh->full[r]);   // both panels, one op
+                    bulk_load(st + kXStageBytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[r]);
+                    if (issued < 64) ET_STAMP(100 + issued);
                 }
-            } else if (lane == 0) {
-                uint8_t* st = smem + (size_t)r * slot_bytes;
-                const uint2 d = need_dir ? sh->dir[kc] : p.first[chunk];
-                const uint32_t bbytes = d.y * 16u;
-                if (ET_GEMM_EXPERIMENT & 9) {
-                    const uint32_t xb = (ET_GEMM_EXPERIMENT & 8) ? 0u : (uint32_t)kXStageBytes;
-                    const uint32_t wb = (ET_GEMM_EXPERIMENT & 1) ? (uint32_t)kHeaderBytes : bbytes;
-                    mbar_expect_tx(&sh->full[r], xb + wb);
-                    if (!(ET_GEMM_EXPERIMENT & 8)) tma_load_3d(st, &tmX, 0, slab * kSlab, kc * (kKC / kPanel), &sh->full[r]);
-                    bulk_load(st + kXStageBytes, p.stream + (size_t)d.x * 16u, wb, &sh->full[r]);
-                } else {
-                mbar_expect_tx(&sh->full[r], kXStageBytes + bbytes);
-                tma_load_3d(st, &tmX, 0, slab * kSlab, kc * (kKC / kPanel), &sh->full[r]);   // both panels, one op
-                bulk_load(st + kXStageBytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[r]);
-                }
-                ET_STAMP(100 + kc);
+                ++issued;
+                if (++r == R) { r = 0; ph ^= 1u; }
             }
-            ++issued;
-            if (++r == R) { r = 0; ph ^= 1u; }
         }
-        if (!dir_ready) __syncwarp();
         // Leaving early: wait (bounded) for the copies still in flight before the CTA exits.
         if (lane == 1 && sh->abort)
             for (int kk = issued > R ? issued - R : 0; kk < issued; ++kk)
@@ -237,17 +216,13 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (warp == 1) {
             tmem_alloc(&sh->tmem_base, 512);
             tmem_relinquish();
-        } else if (warp >= kFirstIssuer) {
-            // this chunk's bias, read again by the epilogue
-            const int col0 = chunk * p.nb * 16;
-            for (int i = tid - 32 * kFirstIssuer; i < p.nb * 16; i += 32 * kIssuers)
-                sh->bias[i] = (col0 + i < p.N) ? p.bias[col0 + i] : __float2half(0.f);
         }
         tc_fence_before();
-        named_barrier_sync(1, kThreads - 32);   // all but the producer: tensor-memory base and bias are visible
+        named_barrier_sync(1, kThreads - 32);   // all but the producer: the tensor-memory base is visible
         tc_fence_after();
         const uint32_t tmem = sh->tmem_base;
-        // Accumulators start at zero: block-rows without tiles are legal and every UMMA accumulates.
+        // Accumulators start at zero: block-rows without tiles are legal and every UMMA accumulates. (After
+        // each tile the epilogue clears them again.)
         if (warp >= kFirstIssuer) {
             const int w = warp - kFirstIssuer;
             const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -258,20 +233,26 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         named_barrier_sync(2, kThreads);        // + the producer's arrive: mbarriers are initialised
         tc_fence_after();
         if (tid == 32) ET_STAMP(2);
+        const int n_items = my_tiles * p.k_chunks;
 
         if (warp < kFirstIssuer) {
             // ---------------- movers: shared memory -> tensor memory copy of the A operand. Two warps take
-            // alternate chunks, so a warp's next wait does not directly follow its own tcgen05.commit.
-            // Lane 1 polls, lane 0 issues and commits: a wait by the thread that has just committed is slow.
+            // alternate chunks; lane 1 polls, lane 0 issues and commits.
             const int m = warp - 1;
-            for (int kc = m; kc < p.k_chunks; kc += kMovers) {
-                const int r = kc % R;
-                const uint32_t ph = (uint32_t)(kc / R) & 1u;
+            int r = m % R, a = m % RA;
+            uint32_t ph = (uint32_t)(m / R) & 1u;
+            for (int it = m; it < n_items; it += kMovers) {
                 if (sh->abort) break;
                 int got = 1;
-                if (lane == 1) got = mbar_wait(&sh->full[r], ph);
+                if (lane == 1) {
+                    got = mbar_wait(&sh->full[r], ph);
+                    if (got && it >= RA) {   // the tensor-memory slot: chunk it - RA must be done
+                        const int prev = it - RA;
+                        got = mbar_wait(&sh->slot_free[prev % R], (uint32_t)(prev / R) & 1u);
+                    }
+                }
                 got = __shfl_sync(0xffffffffu, got, 1);
-                if (m == 0 && lane == 0) ET_STAMP(700 + kc);
+                if (lane == 0 && it < 64) ET_STAMP(700 + it);
                 if (!got) {
                     if (lane == 0) atomicExch(p.err, 12);
                     sh->abort = 1;
@@ -280,120 +261,163 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 tc_fence_after();
                 if (lane == 0) {
                     const uint32_t xa = smem_u32(smem + (size_t)r * slot_bytes);
-                    const uint32_t ta = tmem + a_col0 + r * kSlotCols;
+                    const uint32_t ta = tmem + a_col0 + a * kSlotCols;
 #pragma unroll
-                    for (int sl = 0; sl < ((ET_GEMM_EXPERIMENT & 4) ? 0 : kSlices); ++sl)
+                    for (int sl = 0; sl < kSlices; ++sl)
                         tc_cp_128x256b(ta + sl * 8,
                                        make_smem_desc(xa + (sl >> 2) * kPanelBytes + (sl & 3) * 32, 16, 1024, 2));
-                    umma_commit(&sh->a_ready[r]);
-                    if (m == 0) ET_STAMP(300 + kc);
+                    umma_commit(&sh->a_ready[a]);
+                    if (it < 64) ET_STAMP(300 + it);
                 }
                 __syncwarp();
+                r += kMovers;
+                while (r >= R) { r -= R; ph ^= 1u; }
+                a = (a + kMovers) % RA;
             }
         } else {
-            // ---------------- issuers: one UMMA per kept tile, A from tensor memory
+            // ---------------- issuers: one UMMA per kept tile, A from tensor memory; then the tile's epilogue
             const int w = warp - kFirstIssuer;
-            // B tile descriptor: no swizzle, 128 B between core matrices along K, 256 B along N.
-            const uint64_t b_desc0 = make_smem_desc(0, 128, 256, 0);
-            bool ok = true;
-            int r = 0;
-            uint32_t ph = 0;
-            for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
-                if (sh->abort) { ok = false; break; }
-                // a_ready implies full: the mover waited for the slot's TMA before copying. One lane polls.
-                int got = 1;
-                if (lane == 1) {
-                    got = mbar_wait(&sh->a_ready[r], ph);
-                    if (w == 0) ET_STAMP(500 + kc);
-                }
-                got = __shfl_sync(0xffffffffu, got, 1);
-                if (!got) {
-                    if (lane == 0) atomicExch(p.err, 13);
-                    sh->abort = 1;
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint8_t* blk = smem + (size_t)r * slot_bytes + kXStageBytes;
-                const uint32_t hw = reinterpret_cast<const uint32_t*>(blk)[w];
-                const int e0 = hw & 0xffff, ne = hw >> 16;
-                const uint32_t n_entries = reinterpret_cast<const uint32_t*>(blk)[8];
-                const uint4* ent = reinterpret_cast<const uint4*>(blk + kHeaderBytes) + e0;
-                const uint32_t tiles16 = (smem_u32(blk) + kHeaderBytes + n_entries * 16u) >> 4;
-                const uint32_t abuf = tmem + a_col0 + r * kSlotCols;
-#pragma unroll 4
-                for (int i = 0; i < ne; ++i) {
-                    const uint4 e = ent[i];
-                    if (!(ET_GEMM_EXPERIMENT & 2) && elect_one())
-                        umma_f16_ts(tmem + e.z + ((ET_GEMM_EXPERIMENT & 16) ? (uint32_t)(i & 1) * 128u : 0u), abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
-                }
-                if (elect_one()) umma_commit(&sh->slot_free[r]);
-                if (w == 0 && lane == 0) ET_STAMP(600 + kc);
-                __syncwarp();
-                if (++r == R) { r = 0; ph ^= 1u; }
-            }
-            if (elect_one()) umma_commit(&sh->acc_done);
-            __syncwarp();
-
-            // ---------------- epilogue: TMEM -> registers -> bias / GELU -> fp16 -> swizzled panels -> TMA store.
-            // One round fills one 64-column panel (4 block-rows: two per column half); the panel is stored
-            // while the next round reads tensor memory.
-            if (ok) {
-                int done = 1;
-                if (lane == 0) done = mbar_wait(&sh->acc_done, 0);
-                done = __shfl_sync(0xffffffffu, done, 0);
-                if (!done) {
-                    if (lane == 0) atomicExch(p.err, 14);
-                    sh->abort = 1;
-                    ok = false;
-                }
-            }
-            tc_fence_after();
-            if (w == 0 && lane == 0) ET_STAMP(3);
             const int q = warp & 3;
             const int row = q * 32 + lane;                 // row of the slab = TMEM lane
             const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-            const int npanels = (p.nb + 3) >> 2;
-            for (int pi = 0; pi < npanels; ++pi) {
-                const int lb = pi * 4 + (w >> 2), lb2 = lb + 2;
-                if (ok && lb < p.nb) {
-                    const bool has2 = lb2 < p.nb;
-                    uint32_t acc[2][16];
-                    tmem_ld16(tmem + lane_base + lb * 16, acc[0]);
-                    if (has2) tmem_ld16(tmem + lane_base + lb2 * 16, acc[1]);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        if (u == 1 && !has2) break;
-                        const int l = u ? lb2 : lb;
-                        const half2* bh = reinterpret_cast<const half2*>(sh->bias + l * 16);
-                        uint4 ov[2];
-                        half2* oh = reinterpret_cast<half2*>(ov);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float2 bb = __half22float2(bh[i]);
-                            float v0 = __uint_as_float(acc[u][2 * i]) + bb.x;
-                            float v1 = __uint_as_float(acc[u][2 * i + 1]) + bb.y;
-                            if (p.gelu) {
-                                v0 = gelu_tanh(v0);
-                                v1 = gelu_tanh(v1);
-                            }
-                            oh[i] = __floats2half2_rn(v0, v1);
-                        }
-                        // 16-byte chunks 2*(l%4) and 2*(l%4)+1 of the row, 128-byte swizzle
-                        uint8_t* prow = smem + (size_t)pi * kPanelBytes + row * 128;
-                        const int c0 = (l & 3) * 2;
-                        *reinterpret_cast<uint4*>(prow + (((c0) ^ (row & 7)) << 4)) = ov[0];
-                        *reinterpret_cast<uint4*>(prow + (((c0 + 1) ^ (row & 7)) << 4)) = ov[1];
+            // B tile descriptor: no swizzle, 128 B between core matrices along K, 256 B along N.
+            const uint64_t b_desc0 = make_smem_desc(0, 128, 256, 0);
+            bool ok = true;
+            int r = 0, a = 0;
+            uint32_t pha = 0;
+            int stores = 0;   // output panels handed to TMA so far (panel buffers alternate)
+            for (int tl = 0; tl < my_tiles; ++tl) {
+                const int tile = (int)blockIdx.x + tl * G;
+                const int slab = tile / p.n_chunks, chunk = tile - slab * p.n_chunks;
+                // this tile's bias (read by the epilogue; the barrier below also orders the accumulator clear)
+                {
+                    const int col0 = chunk * p.nb * 16;
+                    for (int i = tid - 32 * kFirstIssuer; i < p.nb * 16; i += 32 * kIssuers)
+                        sh->bias[i] = (col0 + i < p.N) ? p.bias[col0 + i] : __float2half(0.f);
+                }
+                named_barrier_sync(3, 32 * kIssuers);
+                for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
+                    if (sh->abort) {
+                        sh->issuer_abort = 1;
+                        ok = false;
+                        break;
                     }
-                    fence_proxy_async_smem();
+                    // a_ready implies full: the mover waited for the slot's TMA before copying. Lane 1 polls.
+                    int got = 1;
+                    if (lane == 1) {
+                        got = mbar_wait(&sh->a_ready[a], pha);
+                        if (w == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(500 + tl * p.k_chunks + kc);
+                    }
+                    got = __shfl_sync(0xffffffffu, got, 1);
+                    if (!got) {
+                        if (lane == 0) atomicExch(p.err, 13);
+                        sh->abort = 1;
+                        sh->issuer_abort = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint8_t* blk = smem + (size_t)r * slot_bytes + kXStageBytes;
+                    const uint32_t hw = reinterpret_cast<const uint32_t*>(blk)[w];
+                    const int e0 = hw & 0xffff, ne = hw >> 16;
+                    const uint32_t n_entries = reinterpret_cast<const uint32_t*>(blk)[8];
+                    const uint4* ent = reinterpret_cast<const uint4*>(blk + kHeaderBytes) + e0;
+                    const uint32_t tiles16 = (smem_u32(blk) + kHeaderBytes + n_entries * 16u) >> 4;
+                    const uint32_t abuf = tmem + a_col0 + a * kSlotCols;
+#pragma unroll 4
+                    for (int i = 0; i < ne; ++i) {
+                        const uint4 e = ent[i];
+                        if (!(ET_GEMM_EXPERIMENT & 2) && elect_one())
+                            umma_f16_ts(tmem + e.z, abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
+                    }
+                    if (elect_one()) umma_commit(&sh->slot_free[r]);
+                    if (w == 0 && lane == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(600 + tl * p.k_chunks + kc);
+                    __syncwarp();
+                    if (++r == R) r = 0;
+                    if (++a == RA) { a = 0; pha ^= 1u; }
                 }
-                named_barrier_sync(3, 32 * kIssuers);   // the panel is complete
-                if (w == 0 && lane == 0 && !sh->abort) {
-                    const int col = chunk * p.nb * 16 + pi * kPanel;
-                    if (col < p.N) tma_store_2d(&tmY, smem + (size_t)pi * kPanelBytes, col, slab * kSlab);
-                    tma_store_commit();
+                if (elect_one()) umma_commit(&sh->acc_done);
+                __syncwarp();
+
+                // ---------------- epilogue: TMEM -> registers -> bias / GELU -> fp16 -> swizzled panel -> TMA store
+                if (ok) {
+                    int done = 1;
+                    if (lane == 1) done = mbar_wait(&sh->acc_done, (uint32_t)tl & 1u);
+                    done = __shfl_sync(0xffffffffu, done, 1);
+                    if (!done) {
+                        if (lane == 0) atomicExch(p.err, 14);
+                        sh->abort = 1;
+                        sh->issuer_abort = 1;
+                        ok = false;
+                    }
                 }
+                tc_fence_after();
+                if (w == 0 && lane == 0 && tl < 16) ET_STAMP(1400 + tl * 16);
+                const int npanels = (p.nb + 3) >> 2;
+                for (int pi = 0; pi < npanels; ++pi, ++stores) {
+                    uint8_t* pbuf = panels + (size_t)(stores & (p.panel_bufs - 1)) * kPanelBytes;
+                    const int lb = pi * 4 + (w >> 2), lb2 = lb + 2;
+                    uint4 ov[2][2];
+                    const bool has1 = ok && lb < p.nb, has2 = ok && lb2 < p.nb;
+                    if (has1) {
+                        uint32_t acc[2][16];
+                        tmem_ld16(tmem + lane_base + lb * 16, acc[0]);
+                        if (has2) tmem_ld16(tmem + lane_base + lb2 * 16, acc[1]);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            if (u == 1 && !has2) break;
+                            const int l = u ? lb2 : lb;
+                            const half2* bh = reinterpret_cast<const half2*>(sh->bias + l * 16);
+                            half2* oh = reinterpret_cast<half2*>(ov[u]);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float2 bb = __half22float2(bh[i]);
+                                float v0 = __uint_as_float(acc[u][2 * i]) + bb.x;
+                                float v1 = __uint_as_float(acc[u][2 * i + 1]) + bb.y;
+                                if (p.gelu) {
+                                    v0 = gelu_tanh(v0);
+                                    v1 = gelu_tanh(v1);
+                                }
+                                oh[i] = __floats2half2_rn(v0, v1);
+                            }
+                        }
+                    }
+                    // the buffer was handed to TMA one or two panels ago: that store must have finished reading it
+                    if (w == 0 && lane == 0) {
+                        if (p.panel_bufs == 2) tma_store_wait_read_1();
+                        else tma_store_wait_read();
+                    }
+                    named_barrier_sync(3, 32 * kIssuers);
+                    if (has1) {
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            if (u == 1 && !has2) break;
+                            const int l = u ? lb2 : lb;
+                            // 16-byte chunks 2*(l%4) and 2*(l%4)+1 of the row, 128-byte swizzle
+                            uint8_t* prow = pbuf + row * 128;
+                            const int c0 = (l & 3) * 2;
+                            *reinterpret_cast<uint4*>(prow + (((c0) ^ (row & 7)) << 4)) = ov[u][0];
+                            *reinterpret_cast<uint4*>(prow + (((c0 + 1) ^ (row & 7)) << 4)) = ov[u][1];
+                        }
+                        fence_proxy_async_smem();
+                    }
+                    named_barrier_sync(3, 32 * kIssuers);   // the panel is complete
+                    if (w == 0 && lane == 0) {
+                        const int col = chunk * p.nb * 16 + pi * kPanel;
+                        if (!sh->abort && col < p.N) tma_store_2d(&tmY, pbuf, col, slab * kSlab);
+                        tma_store_commit();
+                        if (tl < 16 && pi < 14) ET_STAMP(1400 + tl * 16 + 1 + pi);
+                    }
+                }
+                // clear the accumulators for the next tile (each warp its lane quarter and column half)
+                if (tl + 1 < my_tiles) {
+                    for (int br = (w >> 2); br < p.nb; br += 2) tmem_st16_zero(tmem + lane_base + br * 16);
+                    tmem_st_wait();
+                    tc_fence_before();
+                }
+                if (w == 0 && lane == 0 && tl < 16) ET_STAMP(1400 + tl * 16 + 15);
+                if (sh->issuer_abort) break;
             }
             if (w == 0 && lane == 0) tma_store_wait_read();   // shared memory may go once the stores have read it
         }
@@ -410,7 +434,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 // --------------------------------------------------------------------------------- host side
 
 struct TileWeight {
-    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, slots = 0;
+    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, slots = 0, a_slots = 0, panel_bufs = 1;
     long ntile = 0;
     int size_hint = 0;
     // the caller's arrays, kept so that weights can be concatenated (Q|K|V in one launch) and re-packed
@@ -424,24 +448,42 @@ struct TileWeight {
     size_t stream_bytes = 0;
 };
 
-// Block-rows per CTA. The kernel is bound by what one SM can pull from L2 (the 16 KB activation panel plus
-// the weight block per K chunk), so the estimate is waves x bytes per K chunk; ties go to the larger chunk
-// (fewer passes over the activations).
-static int choose_nb(int n_block_rows, int size_hint, double density) {
+// Block-rows per CTA from a model of the persistent kernel: a slot of the ring takes about 2300 clocks to go
+// round (TMA, tcgen05.cp, UMMAs, commit, poll), R slots are in flight, a chunk cannot be faster than its UMMAs
+// (~10 clocks each with eight issuing warps), and a tile ends with ~800 clocks of epilogue per 64-column panel.
+struct RingShape { int stages, a_slots, panel_bufs; };
+static RingShape ring_shape(int nb, int stage_b_bytes) {
+    const int slot = kXStageBytes + stage_b_bytes;
+    const int avail = kSmemMax - 1024 - (int)sizeof(Shared);
+    RingShape s;
+    s.stages = std::min(kMaxSlots, (avail - kPanelBytes) / slot);
+    s.panel_bufs = avail - s.stages * slot >= 2 * kPanelBytes ? 2 : 1;
+    s.a_slots = std::min(s.stages, (512 - nb * 16) / kSlotCols);
+    return s;
+}
+static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double density) {
     const int slabs = std::max(1, (size_hint + kSlab - 1) / kSlab);
     const int sms = std::max(1, sm_count());
     double best = 0;
     int best_nb = 0;
-    for (int nb : {24, 16, 12, 8}) {
+    for (int nb : {24, 20, 16, 12, 8}) {
         // chunks other than a single one must cover whole 64-column output panels (nb % 4 == 0)
         const int nbe = n_block_rows <= nb ? std::max(n_block_rows, 1) : nb;
         if (nbe > kMaxNB) continue;
-        const long ctas = (long)slabs * ((n_block_rows + nbe - 1) / nbe);
-        const double waves = (double)((ctas + sms - 1) / sms);
-        const double cost = waves * (kXStageBytes + nbe * kSlices * density * 528.0 + 4096.0);
+        const double tiles_per_chunk = nbe * kSlices * density;
+        const int stage_b = (int)((kHeaderBytes + tiles_per_chunk * 1.5 * 528.0 + 1023) / 1024) * 1024;   // worst block ~1.5x mean
+        const RingShape rs = ring_shape(nbe, stage_b);
+        if (rs.stages < 2 || rs.a_slots < 1) continue;
+        const long tiles = (long)slabs * ((n_block_rows + nbe - 1) / nbe);
+        const double per_cta = (double)((tiles + sms - 1) / sms);
+        // stage cycle, tensor-memory slot cycle, UMMA issue, and the SM's share of L2 bandwidth (~64 B/clock)
+        const double t_chunk = std::max({2200.0 / rs.stages, 1100.0 / rs.a_slots, 10.0 * tiles_per_chunk,
+                                         (kXStageBytes + tiles_per_chunk * 528.0) / 64.0});
+        const double t_tile = k_chunks * t_chunk + 800.0 * ((nbe + 3) / 4) + 500.0;
+        const double cost = per_cta * t_tile + 3000.0;
         if (best_nb == 0 || cost < best * 0.999) { best = cost; best_nb = nbe; }
     }
-    return best_nb;
+    return best_nb > 0 ? best_nb : std::min(8, std::max(n_block_rows, 1));
 }
 
 int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, const half* data,
@@ -460,7 +502,7 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     auto* w = new TileWeight();
     w->K = K; w->N = N; w->ntile = ntile; w->size_hint = size_hint;
     const double density = (double)ntile / std::max(1.0, (double)NBR * (K / 16));
-    w->nb = choose_nb(NBR, size_hint, density);
+    w->nb = choose_nb(NBR, (K + kKC - 1) / kKC, size_hint, density);
     if (nb_override > 0) {
         const int nbo = std::min(nb_override, kMaxNB);
         w->nb = NBR <= nbo ? NBR : std::max(4, nbo / 4 * 4);
@@ -521,9 +563,10 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     }
     for (int c = 0; c < w->n_chunks && c < kDirInParams; ++c) w->h_first.push_back(dir[(size_t)c * w->k_chunks]);
     w->stage_b_bytes = (int)((max_block + 1023) / 1024 * 1024);
-    const int slot = kXStageBytes + w->stage_b_bytes;
-    const int tmem_slots = (512 - w->nb * 16) / kSlotCols;
-    w->slots = std::min({kMaxSlots, tmem_slots, (kSmemMax - 1024 - (int)sizeof(Shared)) / slot});
+    {
+        const RingShape rs = ring_shape(w->nb, w->stage_b_bytes);
+        w->slots = rs.stages; w->a_slots = rs.a_slots; w->panel_bufs = rs.panel_bufs;
+    }
     if (w->slots < 2) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
     w->stream_bytes = stream.size();
 
@@ -594,13 +637,13 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     GemmParams p;
     p.dir = w->d_dir; p.stream = w->d_stream; p.Y = Y; p.bias = w->d_bias;
     p.T = T; p.N = w->N; p.k_chunks = w->k_chunks; p.nb = w->nb;
-    p.stage_b_bytes = w->stage_b_bytes; p.slots = w->slots; p.gelu = gelu; p.err = w->d_err;
+    p.n_chunks = w->n_chunks;
+    p.n_tiles = ((T + kSlab - 1) / kSlab) * w->n_chunks;
+    p.stage_b_bytes = w->stage_b_bytes; p.slots = w->slots; p.a_slots = w->a_slots; p.panel_bufs = w->panel_bufs; p.gelu = gelu; p.err = w->d_err;
     p.prof = g_prof;
     for (size_t c = 0; c < w->h_first.size(); ++c) p.first[c] = w->h_first[c];
-    const size_t ring = std::max<size_t>((size_t)w->slots * (kXStageBytes + w->stage_b_bytes),
-                                         (size_t)((w->nb + 3) / 4) * kPanelBytes);
-    const size_t smem = ring + sizeof(Shared) + 1024;
-    dim3 grid((T + kSlab - 1) / kSlab, w->n_chunks);
+    const size_t smem = (size_t)w->slots * (kXStageBytes + w->stage_b_bytes) + (size_t)w->panel_bufs * kPanelBytes + sizeof(Shared) + 1024;
+    dim3 grid(std::min(p.n_tiles, sm_count()));
     const cudaError_t le = launch_pdl(tile_gemm_kernel, grid, dim3(kThreads), smem, st, tm, tmy, p);
     if (le != cudaSuccess) return cuda_status(le, "tile linear launch");
     return cuda_status(cudaGetLastError(), "tile linear launch");
