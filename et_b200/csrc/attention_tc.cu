@@ -442,9 +442,9 @@ int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, in
     CUtensorMap tq, tk, tv;
     const uint64_t rows = (uint64_t)total_tokens;
     // the column extent covers all heads of the operand; Q/K/V may be slices of one fused [tokens x 3 d_model] buffer
-    if (!make_tmap_2d_f16(&tq, Q, rows, (uint64_t)d_model, (uint64_t)q_pitch, kBQ, kHD, true) ||
-        !make_tmap_2d_f16(&tk, K, rows, (uint64_t)d_model, (uint64_t)q_pitch, kBK, kHD, true) ||
-        !make_tmap_2d_f16(&tv, V, rows, (uint64_t)d_model, (uint64_t)v_pitch, kBK, kHD, true))
+    if (!make_tmap_2d_f16(&tq, Q, rows, (uint64_t)d_model, (uint64_t)q_pitch, kBQ, kHD, 128) ||
+        !make_tmap_2d_f16(&tk, K, rows, (uint64_t)d_model, (uint64_t)q_pitch, kBK, kHD, 128) ||
+        !make_tmap_2d_f16(&tv, V, rows, (uint64_t)d_model, (uint64_t)v_pitch, kBK, kHD, 128))
         return fail(ET_ERR_CUDA, "attention: cuTensorMapEncodeTiled failed");
     TcParams p;
     p.Z = Z; p.mask = mask; p.cu_seqlens = cu_seqlens; p.valid_lens = valid_lens;

@@ -55,6 +55,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// The same for a wait that is expected to last: the thread asks to be suspended for up to `hint_ns` per try, so
+// that its polling does not take issue slots from the warps it is waiting for.
+#ifndef ET_WAIT_MODE
+#define ET_WAIT_MODE 1
+#endif
+__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity) {
+#if ET_WAIT_MODE == 1
+    for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n.reg .pred P;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n"
+            "selp.u32 %0, 1, 0, P;\n}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity), "r"(4000u)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+#elif ET_WAIT_MODE == 2
+    for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(40);
+    }
+    return false;
+#else
+    return mbar_wait(bar, parity);
+#endif
+}
 
 // ------------------------------------------------------------------ TMA
 __device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y,

@@ -24,6 +24,7 @@
 // Every mbarrier wait is bounded; a wait that gives up records a code in the error word, the CTA
 // stops issuing, frees its tensor memory and returns.
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -44,12 +45,14 @@ constexpr int kPanel = 64;          // columns per panel
 constexpr int kSlices = kKC / 16;   // UMMA K steps per chunk
 constexpr int kMaxNB = 24;          // block-rows per CTA (384 accumulator columns)
 constexpr int kSlotCols = kKC / 2;  // TMEM columns of one A slot
-constexpr int kMaxSlots = 4;
+constexpr int kMaxRing = 6;           // barriers per ring
 constexpr int kIssuers = 8;         // UMMA-issuing warps
-constexpr int kMovers = 2;          // tcgen05.cp-issuing warps, alternating chunks
+constexpr int kMovers = 2;          // tcgen05.cp-issuing warps, taking chunks in turn
 constexpr int kFirstIssuer = 1 + kMovers;
 constexpr int kThreads = 32 * (1 + kMovers + kIssuers);
 constexpr int kDirInParams = 32;    // directory entries of each chunk's first block travel as kernel parameters
+constexpr int kUnitCols = 32;          // columns per epilogue store
+constexpr int kUnitBytes = 32 * kUnitCols * 2;   // one warp's staging buffer: 32 rows x 32 columns
 constexpr int kPanelBytes = kSlab * kPanel * 2;   // 16 KB
 constexpr int kXStageBytes = kSlab * kKC * 2;     // 32 KB
 constexpr int kHeaderBytes = 64;
@@ -61,7 +64,7 @@ struct GemmParams {
     const uint8_t* stream;   // packed blocks
     half* Y;
     const half* bias;
-    int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, slots, a_slots, panel_bufs, gelu;
+    int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, stages, a_slots, epi_bufs, gelu;
     int* err;
     uint2 first[kDirInParams];   // dir[chunk][0] for chunk < kDirInParams: no global load before the first TMA
     long long* prof;         // optional per-role clock64 stamps of CTA (0,0) (ET_GEMM_PROFILE builds only)
@@ -96,25 +99,34 @@ __device__ __forceinline__ void tmem_st16_zero(uint32_t taddr) {
         "r"(0u)
         : "memory");
 }
-__device__ __forceinline__ float tanh_fast(float x) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-__device__ __forceinline__ float gelu_tanh(float x) {
-    return 0.5f * x * (1.0f + tanh_fast(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+// tanh-GELU of two values, the tanh on the packed fp16 pair: one special-function op per two elements (the
+// special-function unit, 16 results per clock per SM, is what bounds a 128 x 384 GELU epilogue). The argument is
+// clamped to +-9 (tanh is 1 to fp16 precision long before) so that the fp16 pack cannot overflow.
+__device__ __forceinline__ half2 gelu_tanh_pair(float a, float b) {
+    float ua = 0.7978845608028654f * a * fmaf(0.044715f * a, a, 1.0f);
+    float ub = 0.7978845608028654f * b * fmaf(0.044715f * b, b, 1.0f);
+    ua = fminf(fmaxf(ua, -9.0f), 9.0f);
+    ub = fminf(fmaxf(ub, -9.0f), 9.0f);
+    const half2 u = __floats2half2_rn(ua, ub);
+    uint32_t t;
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(*reinterpret_cast<const uint32_t*>(&u)));
+    const float2 tf = __half22float2(*reinterpret_cast<const half2*>(&t));
+    const float ha = 0.5f * a, hb = 0.5f * b;
+    return __floats2half2_rn(fmaf(ha, tf.x, ha), fmaf(hb, tf.y, hb));
 }
 
 struct Shared {
-    uint64_t full[kMaxSlots];       // stage filled: two activation panels + the weight block (TMA)
-    uint64_t a_ready[kMaxSlots];    // the chunk's activations are in their tensor-memory slot (mover commit)
-    uint64_t slot_free[kMaxSlots];  // every issuer's UMMAs on the stage have completed (8 commits)
-    uint64_t acc_done;              // 8 issuer commits after a tile's last chunk
+    uint64_t full[kMaxRing];      // [chunk % stages]  the chunk's activations and weight block have landed (TMA)
+    uint64_t done[kMaxRing];      // [chunk % stages]  every issuer's UMMAs on the chunk have completed (8 commits)
+    uint64_t a_ready[kMaxRing];   // [chunk % a_slots] the chunk's activations are in tensor memory (mover commit)
+    uint64_t acc_done;            // 8 issuer commits after a tile's last chunk
     uint32_t tmem_base;
-    volatile int abort;         // any role gave up: everybody winds down
-    volatile int issuer_abort;  // written by issuer warps only, before a tile's last named barrier, and read
-                                // after it: all eight warps leave the tile loop at the same tile
-    __align__(16) half bias[kMaxNB * 16];  // the current tile's bias
+    volatile int abort;            // any role gave up: everybody winds down
+    volatile int issuer_abort[2];  // [tile parity]: set by an issuer warp that gives up during a tile, read by
+                                   // all of them after the named barrier that opens the next tile, so that
+                                   // the eight warps leave the tile loop at the same tile
+    __align__(16) half bias[2][kMaxNB * 16];  // [tile parity]: a warp may still convert tile t while another
+                                              // stages the bias of tile t + 1
 };
 
 __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
@@ -123,27 +135,70 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 __device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
-__device__ __forceinline__ void tma_store_wait_read_1() {
-    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+
+// One 32-column unit of the epilogue, in three steps so that two units can be in flight per warp.
+__device__ __forceinline__ void epi_load(uint32_t taddr, bool two, uint32_t (&acc)[32]) {
+    if (two) {
+        tmem_ld32(taddr, acc);
+    } else {
+        uint32_t lo[16];
+        tmem_ld16(taddr, lo);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            acc[i] = lo[i];
+            acc[16 + i] = 0u;
+        }
+    }
+}
+template <bool kGelu>
+__device__ __forceinline__ void epi_convert(const uint32_t (&acc)[32], const half* bias, bool two, uint4 (&ov)[4]) {
+    uint4 bv[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        bv[c] = (two || c < 2) ? reinterpret_cast<const uint4*>(bias)[c] : make_uint4(0u, 0u, 0u, 0u);
+    const half2* bh = reinterpret_cast<const half2*>(bv);
+    half2* oh = reinterpret_cast<half2*>(ov);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float2 bb = __half22float2(bh[i]);
+        const float v0 = __uint_as_float(acc[2 * i]) + bb.x;
+        const float v1 = __uint_as_float(acc[2 * i + 1]) + bb.y;
+        if constexpr (kGelu) oh[i] = gelu_tanh_pair(v0, v1);
+        else oh[i] = __floats2half2_rn(v0, v1);
+    }
+}
+// Row `lane` of a 32 x 32 unit: four 16-byte chunks under the 64-byte swizzle (chunk ^= (row / 2) % 4).
+__device__ __forceinline__ void epi_write(uint8_t* buf, int lane, const uint4 (&ov)[4]) {
+    uint8_t* prow = buf + lane * 64;
+    const int x = (lane >> 1) & 3;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(prow + ((c ^ x) << 4)) = ov[c];
 }
 
 // Persistent: CTA c processes tiles c, c + gridDim.x, ... (tile = slab * n_chunks + chunk, so CTAs that run
-// together share activations in L2). The slot ring runs on across tiles: while the issuer warps convert and
-// store one tile, the producer and the movers already stage the first chunks of the next.
+// together share activations in L2). One chunk counter runs on across tiles and indexes two rings:
+//   * `stages` shared-memory stages (32 KB of activations + the weight block), free when the chunk's UMMAs
+//     have completed (they read the tiles there);
+//   * a_slots <= stages tensor-memory slots for the A operand, free when the chunk a_slots before is done,
+//     which the movers read from the `done` barriers with that lag.
+// Every role does as few serial barrier operations per chunk as possible: on this part a wait on a completed
+// mbarrier, a tcgen05.cp or a TMA issue each cost a warp 100-250 clocks, and the chunk period is the longest
+// such chain (a version with a separate, earlier-freed activation ring needed a second wait per chunk in the
+// producer and a second commit in the movers and was 20-50 % slower).
+// While the issuer warps convert and store one tile, the producer and the movers stage the next tile's chunks.
+template <bool kGelu>
 __global__ void __launch_bounds__(kThreads, 1)
 tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int slot_bytes = kXStageBytes + p.stage_b_bytes;   // multiple of 1024
-    uint8_t* panels = smem + (size_t)p.slots * slot_bytes;   // one or two 16 KB output panels
-    Shared* sh = reinterpret_cast<Shared*>(panels + p.panel_bufs * kPanelBytes);
+    const int DB = p.stages, RA = p.a_slots;
+    const int slot_bytes = kXStageBytes + p.stage_b_bytes;   // multiple of 1024: activations, then the weight block
+    uint8_t* const xbase = smem;
+    uint8_t* const bbase = smem + kXStageBytes;
+    uint8_t* const epi = smem + (size_t)DB * slot_bytes;               // 8 warps x epi_bufs x 2 KB
+    Shared* sh = reinterpret_cast<Shared*>(epi + p.epi_bufs * kIssuers * kUnitBytes);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // Two rings with one chunk counter: R shared-memory stages (activations + weight block; a stage is free
-    // once the chunk's UMMAs have completed, because they read the weights from it) and RA <= R tensor-memory
-    // slots for the A operand. A chunk's tensor-memory slot is free when the chunk RA before it is done, which
-    // the movers read from the same slot_free barriers with a lag.
-    const int R = p.slots, RA = p.a_slots;
     const int G = gridDim.x;
     const uint32_t a_col0 = 512u - (uint32_t)(RA * kSlotCols);
     const int my_tiles = (p.n_tiles - (int)blockIdx.x + G - 1) / G;
@@ -151,19 +206,17 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     pdl_launch_dependents();   // the next kernel may set itself up on idle SMs while this one runs
 
     if (warp == 0) {
-        // ---------------- producer warp: lane 0 issues the copies, lane 1 polls slot_free (a wait by the thread
-        // that has just issued a bulk copy costs several hundred clocks)
-        {
-            // one barrier per lane
-            if (lane < kMaxSlots) mbar_init(&sh->full[lane], 1);
-            else if (lane < 2 * kMaxSlots) mbar_init(&sh->a_ready[lane - kMaxSlots], 1);
-            else if (lane < 3 * kMaxSlots) mbar_init(&sh->slot_free[lane - 2 * kMaxSlots], kIssuers);
-            else if (lane == 3 * kMaxSlots) mbar_init(&sh->acc_done, kIssuers);
-            if (lane <= 3 * kMaxSlots) fence_mbar_init();
-            if (lane == 0) {
-                sh->abort = 0;
-                sh->issuer_abort = 0;
-            }
+        // ---------------- producer warp: lane 0 issues the copies, lane 1 polls (a wait by the thread that has
+        // just issued a bulk copy costs several hundred clocks)
+        if (lane < kMaxRing) mbar_init(&sh->full[lane], 1);
+        else if (lane < 2 * kMaxRing) mbar_init(&sh->done[lane - kMaxRing], kIssuers);
+        else if (lane < 3 * kMaxRing) mbar_init(&sh->a_ready[lane - 2 * kMaxRing], 1);
+        else if (lane == 3 * kMaxRing) mbar_init(&sh->acc_done, kIssuers);
+        if (lane <= 3 * kMaxRing) fence_mbar_init();
+        if (lane == 0) {
+            sh->abort = 0;
+            sh->issuer_abort[0] = 0;
+            sh->issuer_abort[1] = 0;
         }
         __syncwarp();
         named_barrier_arrive(2, kThreads);   // barriers are initialised: release the other warps
@@ -171,8 +224,8 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // Everything above touched only this kernel's own resources. The activations may still be in the making:
         // wait for the preceding kernels before the first copy (lane 0 issues them all).
         if (lane == 0) pdl_wait();
-        int issued = 0, r = 0;
-        uint32_t ph = 0;
+        int issued = 0, bs = 0;
+        uint32_t phb = 0;
         bool alive = true;
         for (int tl = 0; tl < my_tiles && alive; ++tl) {
             const int tile = (int)blockIdx.x + tl * G;
@@ -185,7 +238,8 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 const uint2 d = dnext;
                 if (lane == 0 && kc + 1 < p.k_chunks) dnext = __ldg(gdir + kc + 1);
                 int go = 1;
-                if (lane == 1) go = (!sh->abort && mbar_wait(&sh->slot_free[r], ph ^ 1u)) ? 1 : 0;
+                if (lane == 1)
+                    go = (!sh->abort && mbar_wait(&sh->done[bs], phb ^ 1u)) ? 1 : 0;
                 go = __shfl_sync(0xffffffffu, go, 1);
                 if (lane == 0 && issued < 64) ET_STAMP(900 + issued);
                 if (!go) {
@@ -197,21 +251,21 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     break;
                 }
                 if (lane == 0) {
-                    uint8_t* st = smem + (size_t)r * slot_bytes;
                     const uint32_t bbytes = d.y * 16u;
-                    mbar_expect_tx(&sh->full[r], kXStageBytes + bbytes);
-                    tma_load_3d(st, &tmX, 0, slab * kSlab, kc * (kKC / kPanel), &sh->full[r]);   // both panels, one op
-                    bulk_load(st + kXStageBytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[r]);
+                    mbar_expect_tx(&sh->full[bs], kXStageBytes + bbytes);
+                    tma_load_3d(xbase + (size_t)bs * slot_bytes, &tmX, 0, slab * kSlab, kc * (kKC / kPanel),
+                                &sh->full[bs]);   // both panels, one op
+                    bulk_load(bbase + (size_t)bs * slot_bytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[bs]);
                     if (issued < 64) ET_STAMP(100 + issued);
                 }
                 ++issued;
-                if (++r == R) { r = 0; ph ^= 1u; }
+                if (++bs == DB) { bs = 0; phb ^= 1u; }
             }
         }
         // Leaving early: wait (bounded) for the copies still in flight before the CTA exits.
         if (lane == 1 && sh->abort)
-            for (int kk = issued > R ? issued - R : 0; kk < issued; ++kk)
-                mbar_wait(&sh->full[kk % R], (uint32_t)(kk / R) & 1u);
+            for (int kk = issued > DB ? issued - DB : 0; kk < issued; ++kk)
+                mbar_wait(&sh->full[kk % DB], (uint32_t)(kk / DB) & 1u);
     } else {
         if (warp == 1) {
             tmem_alloc(&sh->tmem_base, 512);
@@ -222,7 +276,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         tc_fence_after();
         const uint32_t tmem = sh->tmem_base;
         // Accumulators start at zero: block-rows without tiles are legal and every UMMA accumulates. (After
-        // each tile the epilogue clears them again.)
+        // each tile the epilogue clears what it has read.)
         if (warp >= kFirstIssuer) {
             const int w = warp - kFirstIssuer;
             const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -236,19 +290,21 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         const int n_items = my_tiles * p.k_chunks;
 
         if (warp < kFirstIssuer) {
-            // ---------------- movers: shared memory -> tensor memory copy of the A operand. Two warps take
-            // alternate chunks; lane 1 polls, lane 0 issues and commits.
+            // ---------------- movers: shared memory -> tensor memory copy of the A operand. The mover warps take
+            // chunks in turn (a warp needs ~1500 clocks per chunk: two barrier waits, eight tcgen05.cp, two
+            // commits); lane 1 polls, lane 0 issues and commits.
             const int m = warp - 1;
-            int r = m % R, a = m % RA;
-            uint32_t ph = (uint32_t)(m / R) & 1u;
+            int bs = m % DB, a = m % RA;
+            uint32_t phb = (uint32_t)(m / DB) & 1u;
             for (int it = m; it < n_items; it += kMovers) {
                 if (sh->abort) break;
                 int got = 1;
                 if (lane == 1) {
-                    got = mbar_wait(&sh->full[r], ph);
-                    if (got && it >= RA) {   // the tensor-memory slot: chunk it - RA must be done
+                    got = mbar_wait(&sh->full[bs], phb);
+                    // the tensor-memory slot: the chunk a_slots before this one must be done
+                    if (got && it >= RA) {
                         const int prev = it - RA;
-                        got = mbar_wait(&sh->slot_free[prev % R], (uint32_t)(prev / R) & 1u);
+                        got = mbar_wait(&sh->done[prev % DB], (uint32_t)(prev / DB) & 1u);
                     }
                 }
                 got = __shfl_sync(0xffffffffu, got, 1);
@@ -260,49 +316,58 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 }
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t xa = smem_u32(smem + (size_t)r * slot_bytes);
+                    const uint32_t xa = smem_u32(xbase + (size_t)bs * slot_bytes);
                     const uint32_t ta = tmem + a_col0 + a * kSlotCols;
+                    if (!(ET_GEMM_EXPERIMENT & 4)) {
 #pragma unroll
-                    for (int sl = 0; sl < kSlices; ++sl)
-                        tc_cp_128x256b(ta + sl * 8,
-                                       make_smem_desc(xa + (sl >> 2) * kPanelBytes + (sl & 3) * 32, 16, 1024, 2));
+                        for (int sl = 0; sl < kSlices; ++sl)
+                            tc_cp_128x256b(ta + sl * 8,
+                                           make_smem_desc(xa + (sl >> 2) * kPanelBytes + (sl & 3) * 32, 16, 1024, 2));
+                    }
                     umma_commit(&sh->a_ready[a]);
                     if (it < 64) ET_STAMP(300 + it);
                 }
                 __syncwarp();
-                r += kMovers;
-                while (r >= R) { r -= R; ph ^= 1u; }
+                bs += kMovers;
+                while (bs >= DB) { bs -= DB; phb ^= 1u; }
                 a = (a + kMovers) % RA;
             }
         } else {
             // ---------------- issuers: one UMMA per kept tile, A from tensor memory; then the tile's epilogue
             const int w = warp - kFirstIssuer;
-            const int q = warp & 3;
-            const int row = q * 32 + lane;                 // row of the slab = TMEM lane
+            const int q = warp & 3;   // the TMEM lane quarter this warp may read: rows 32q .. 32q + 31 of the slab
+            const int h = w >> 2;     // which of the two warps of this row quarter
             const uint32_t lane_base = (uint32_t)(q * 32) << 16;
             // B tile descriptor: no swizzle, 128 B between core matrices along K, 256 B along N.
             const uint64_t b_desc0 = make_smem_desc(0, 128, 256, 0);
+            // this warp's output staging: 32 rows x 32 columns (64-byte rows, 64-byte swizzle), one or two buffers
+            uint8_t* const buf0 = epi + (size_t)w * p.epi_bufs * kUnitBytes;
+            uint8_t* const buf1 = buf0 + kUnitBytes;
+            const int ustep = 2 * p.epi_bufs;
             bool ok = true;
-            int r = 0, a = 0;
+            int bs = 0, a = 0;
             uint32_t pha = 0;
-            int stores = 0;   // output panels handed to TMA so far (panel buffers alternate)
             for (int tl = 0; tl < my_tiles; ++tl) {
                 const int tile = (int)blockIdx.x + tl * G;
                 const int slab = tile / p.n_chunks, chunk = tile - slab * p.n_chunks;
-                // this tile's bias (read by the epilogue; the barrier below also orders the accumulator clear)
+                half* const tbias = sh->bias[tl & 1];
                 {
                     const int col0 = chunk * p.nb * 16;
                     for (int i = tid - 32 * kFirstIssuer; i < p.nb * 16; i += 32 * kIssuers)
-                        sh->bias[i] = (col0 + i < p.N) ? p.bias[col0 + i] : __float2half(0.f);
+                        tbias[i] = (col0 + i < p.N) ? p.bias[col0 + i] : __float2half(0.f);
                 }
+                // One rendezvous per tile: the bias is staged, every warp has cleared its accumulator columns,
+                // and a warp that gave up in the previous tile is seen by all.
                 named_barrier_sync(3, 32 * kIssuers);
+                if (tl > 0 && sh->issuer_abort[(tl - 1) & 1]) break;
+                tc_fence_after();
                 for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
                     if (sh->abort) {
-                        sh->issuer_abort = 1;
+                        sh->issuer_abort[tl & 1] = 1;
                         ok = false;
                         break;
                     }
-                    // a_ready implies full: the mover waited for the slot's TMA before copying. Lane 1 polls.
+                    // a_ready implies full: the movers waited for the chunk's TMA before copying. Lane 1 polls.
                     int got = 1;
                     if (lane == 1) {
                         got = mbar_wait(&sh->a_ready[a], pha);
@@ -312,12 +377,12 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     if (!got) {
                         if (lane == 0) atomicExch(p.err, 13);
                         sh->abort = 1;
-                        sh->issuer_abort = 1;
+                        sh->issuer_abort[tl & 1] = 1;
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint8_t* blk = smem + (size_t)r * slot_bytes + kXStageBytes;
+                    const uint8_t* blk = bbase + (size_t)bs * slot_bytes;
                     const uint32_t hw = reinterpret_cast<const uint32_t*>(blk)[w];
                     const int e0 = hw & 0xffff, ne = hw >> 16;
                     const uint32_t n_entries = reinterpret_cast<const uint32_t*>(blk)[8];
@@ -330,96 +395,74 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                         if (!(ET_GEMM_EXPERIMENT & 2) && elect_one())
                             umma_f16_ts(tmem + e.z, abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
                     }
-                    if (elect_one()) umma_commit(&sh->slot_free[r]);
+                    if (elect_one()) umma_commit(&sh->done[bs]);
                     if (w == 0 && lane == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(600 + tl * p.k_chunks + kc);
                     __syncwarp();
-                    if (++r == R) r = 0;
+                    if (++bs == DB) bs = 0;
                     if (++a == RA) { a = 0; pha ^= 1u; }
                 }
                 if (elect_one()) umma_commit(&sh->acc_done);
                 __syncwarp();
 
-                // ---------------- epilogue: TMEM -> registers -> bias / GELU -> fp16 -> swizzled panel -> TMA store
+                // ---------------- epilogue, warp by warp with no rendezvous: the two warps of a row quarter take
+                // alternate 32-column units, two at a time where there are two staging buffers:
+                // TMEM -> registers -> bias / GELU -> fp16 -> the warp's own swizzled buffer -> TMA store.
                 if (ok) {
-                    int done = 1;
-                    if (lane == 1) done = mbar_wait(&sh->acc_done, (uint32_t)tl & 1u);
-                    done = __shfl_sync(0xffffffffu, done, 1);
-                    if (!done) {
+                    int fin = 1;
+                    if (lane == 1) fin = mbar_wait(&sh->acc_done, (uint32_t)tl & 1u);
+                    fin = __shfl_sync(0xffffffffu, fin, 1);
+                    if (!fin) {
                         if (lane == 0) atomicExch(p.err, 14);
                         sh->abort = 1;
-                        sh->issuer_abort = 1;
+                        sh->issuer_abort[tl & 1] = 1;
                         ok = false;
                     }
                 }
                 tc_fence_after();
                 if (w == 0 && lane == 0 && tl < 16) ET_STAMP(1400 + tl * 16);
-                const int npanels = (p.nb + 3) >> 2;
-                for (int pi = 0; pi < npanels; ++pi, ++stores) {
-                    uint8_t* pbuf = panels + (size_t)(stores & (p.panel_bufs - 1)) * kPanelBytes;
-                    const int lb = pi * 4 + (w >> 2), lb2 = lb + 2;
-                    uint4 ov[2][2];
-                    const bool has1 = ok && lb < p.nb, has2 = ok && lb2 < p.nb;
-                    if (has1) {
-                        uint32_t acc[2][16];
-                        tmem_ld16(tmem + lane_base + lb * 16, acc[0]);
-                        if (has2) tmem_ld16(tmem + lane_base + lb2 * 16, acc[1]);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-                            if (u == 1 && !has2) break;
-                            const int l = u ? lb2 : lb;
-                            const half2* bh = reinterpret_cast<const half2*>(sh->bias + l * 16);
-                            half2* oh = reinterpret_cast<half2*>(ov[u]);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const float2 bb = __half22float2(bh[i]);
-                                float v0 = __uint_as_float(acc[u][2 * i]) + bb.x;
-                                float v1 = __uint_as_float(acc[u][2 * i + 1]) + bb.y;
-                                if (p.gelu) {
-                                    v0 = gelu_tanh(v0);
-                                    v1 = gelu_tanh(v1);
-                                }
-                                oh[i] = __floats2half2_rn(v0, v1);
-                            }
+                const int units = (p.nb + 1) >> 1;
+                const bool more = tl + 1 < my_tiles;
+                const int col0 = chunk * p.nb * 16, row0 = slab * kSlab + q * 32;
+                for (int u = h; u < units && ok; u += ustep) {
+                    const int u2 = u + 2;
+                    const bool second = p.epi_bufs == 2 && u2 < units;
+                    const bool two_a = u * 2 + 1 < p.nb, two_b = u2 * 2 + 1 < p.nb;
+                    uint32_t acc_a[32], acc_b[32];
+                    epi_load(tmem + lane_base + u * 32, two_a, acc_a);
+                    if (second) epi_load(tmem + lane_base + u2 * 32, two_b, acc_b);
+                    tmem_ld_wait();
+                    if (more) {   // clear what was just read, for the next tile
+                        tmem_st16_zero(tmem + lane_base + u * 32);
+                        if (two_a) tmem_st16_zero(tmem + lane_base + u * 32 + 16);
+                        if (second) {
+                            tmem_st16_zero(tmem + lane_base + u2 * 32);
+                            if (two_b) tmem_st16_zero(tmem + lane_base + u2 * 32 + 16);
                         }
                     }
-                    // the buffer was handed to TMA one or two panels ago: that store must have finished reading it
-                    if (w == 0 && lane == 0) {
-                        if (p.panel_bufs == 2) tma_store_wait_read_1();
-                        else tma_store_wait_read();
-                    }
-                    named_barrier_sync(3, 32 * kIssuers);
-                    if (has1) {
-#pragma unroll
-                        for (int u = 0; u < 2; ++u) {
-                            if (u == 1 && !has2) break;
-                            const int l = u ? lb2 : lb;
-                            // 16-byte chunks 2*(l%4) and 2*(l%4)+1 of the row, 128-byte swizzle
-                            uint8_t* prow = pbuf + row * 128;
-                            const int c0 = (l & 3) * 2;
-                            *reinterpret_cast<uint4*>(prow + (((c0) ^ (row & 7)) << 4)) = ov[u][0];
-                            *reinterpret_cast<uint4*>(prow + (((c0 + 1) ^ (row & 7)) << 4)) = ov[u][1];
-                        }
-                        fence_proxy_async_smem();
-                    }
-                    named_barrier_sync(3, 32 * kIssuers);   // the panel is complete
-                    if (w == 0 && lane == 0) {
-                        const int col = chunk * p.nb * 16 + pi * kPanel;
-                        if (!sh->abort && col < p.N) tma_store_2d(&tmY, pbuf, col, slab * kSlab);
+                    uint4 ov_a[4], ov_b[4];
+                    epi_convert<kGelu>(acc_a, tbias + u * 32, two_a, ov_a);
+                    if (second) epi_convert<kGelu>(acc_b, tbias + u2 * 32, two_b, ov_b);
+                    // the buffers' previous stores must have finished reading them (lane 0 issued them)
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+                    epi_write(buf0, lane, ov_a);
+                    if (second) epi_write(buf1, lane, ov_b);
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (col0 + u * kUnitCols < p.N) tma_store_2d(&tmY, buf0, col0 + u * kUnitCols, row0);
+                        if (second && col0 + u2 * kUnitCols < p.N) tma_store_2d(&tmY, buf1, col0 + u2 * kUnitCols, row0);
                         tma_store_commit();
-                        if (tl < 16 && pi < 14) ET_STAMP(1400 + tl * 16 + 1 + pi);
+                        if (w == 0 && tl < 16 && (u >> 2) < 14) ET_STAMP(1400 + tl * 16 + 1 + (u >> 2));
                     }
                 }
-                // clear the accumulators for the next tile (each warp its lane quarter and column half)
-                if (tl + 1 < my_tiles) {
-                    for (int br = (w >> 2); br < p.nb; br += 2) tmem_st16_zero(tmem + lane_base + br * 16);
+                if (more) {
                     tmem_st_wait();
                     tc_fence_before();
                 }
                 if (w == 0 && lane == 0 && tl < 16) ET_STAMP(1400 + tl * 16 + 15);
-                if (sh->issuer_abort) break;
             }
-            if (w == 0 && lane == 0) tma_store_wait_read();   // shared memory may go once the stores have read it
+            if (lane == 0) tma_store_wait_read();   // shared memory may go once the stores have read it
         }
     }
     tc_fence_before();
@@ -434,7 +477,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 // --------------------------------------------------------------------------------- host side
 
 struct TileWeight {
-    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, slots = 0, a_slots = 0, panel_bufs = 1;
+    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, stages = 0, a_slots = 0, epi_bufs = 1;
     long ntile = 0;
     int size_hint = 0;
     // the caller's arrays, kept so that weights can be concatenated (Q|K|V in one launch) and re-packed
@@ -448,19 +491,28 @@ struct TileWeight {
     size_t stream_bytes = 0;
 };
 
-// Block-rows per CTA from a model of the persistent kernel: a slot of the ring takes about 2300 clocks to go
-// round (TMA, tcgen05.cp, UMMAs, commit, poll), R slots are in flight, a chunk cannot be faster than its UMMAs
-// (~10 clocks each with eight issuing warps), and a tile ends with ~800 clocks of epilogue per 64-column panel.
-struct RingShape { int stages, a_slots, panel_bufs; };
+// Ring depth for a chunk shape: as many stages as shared memory holds (at most four: beyond that the ring is
+// no longer what bounds the chunk period), with two epilogue staging buffers per warp when they do not cost a
+// stage. A stage goes round in ~4000 clocks (TMA, tcgen05.cp, UMMAs, and the polls between them), a
+// tensor-memory slot in ~2000.
+struct RingShape { int stages, a_slots, epi_bufs; double period; };
+// Tuning experiments: {block-rows per CTA, stages, unused, staging buffers}, 0 = automatic.
+static int g_tune[4] = {0, 0, 0, 0};
 static RingShape ring_shape(int nb, int stage_b_bytes) {
+    const int tmem_slots = std::min(kMaxRing, (512 - nb * 16) / kSlotCols);
     const int slot = kXStageBytes + stage_b_bytes;
-    const int avail = kSmemMax - 1024 - (int)sizeof(Shared);
-    RingShape s;
-    s.stages = std::min(kMaxSlots, (avail - kPanelBytes) / slot);
-    s.panel_bufs = avail - s.stages * slot >= 2 * kPanelBytes ? 2 : 1;
-    s.a_slots = std::min(s.stages, (512 - nb * 16) / kSlotCols);
-    return s;
+    const int avail1 = kSmemMax - 1024 - (int)sizeof(Shared) - kIssuers * kUnitBytes;
+    const int cap = g_tune[1] > 0 ? std::min(g_tune[1], kMaxRing) : 4;
+    RingShape r;
+    r.stages = std::min(cap, avail1 / slot);
+    r.epi_bufs = (avail1 - r.stages * slot >= kIssuers * kUnitBytes && g_tune[3] != 1) ? 2 : 1;
+    r.a_slots = std::min(r.stages, tmem_slots);
+    r.period = r.stages >= 1 && r.a_slots >= 1 ? std::max(4000.0 / r.stages, 2000.0 / r.a_slots) : 1e30;
+    return r;
 }
+// Block-rows per CTA from a model of the persistent kernel: a chunk takes the ring period, or its UMMAs (~10
+// clocks each with eight issuing warps), or its share of L2 bandwidth (~64 bytes per clock per SM), whichever
+// is longest; a tile ends with an epilogue of ~350 clocks per 32 columns and warp.
 static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double density) {
     const int slabs = std::max(1, (size_hint + kSlab - 1) / kSlab);
     const int sms = std::max(1, sm_count());
@@ -471,15 +523,17 @@ static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double densi
         const int nbe = n_block_rows <= nb ? std::max(n_block_rows, 1) : nb;
         if (nbe > kMaxNB) continue;
         const double tiles_per_chunk = nbe * kSlices * density;
-        const int stage_b = (int)((kHeaderBytes + tiles_per_chunk * 1.5 * 528.0 + 1023) / 1024) * 1024;   // worst block ~1.5x mean
+        // the largest block of a Bernoulli pattern: mean + 3 standard deviations
+        const double tiles_max = std::min((double)nbe * kSlices,
+                                          tiles_per_chunk + 3.0 * std::sqrt(nbe * kSlices * density * (1.0 - density)));
+        const int stage_b = (int)((kHeaderBytes + tiles_max * 528.0 + 1023) / 1024) * 1024;
         const RingShape rs = ring_shape(nbe, stage_b);
         if (rs.stages < 2 || rs.a_slots < 1) continue;
         const long tiles = (long)slabs * ((n_block_rows + nbe - 1) / nbe);
         const double per_cta = (double)((tiles + sms - 1) / sms);
-        // stage cycle, tensor-memory slot cycle, UMMA issue, and the SM's share of L2 bandwidth (~64 B/clock)
-        const double t_chunk = std::max({2200.0 / rs.stages, 1100.0 / rs.a_slots, 10.0 * tiles_per_chunk,
+        const double t_chunk = std::max({rs.period, 10.0 * tiles_per_chunk,
                                          (kXStageBytes + tiles_per_chunk * 528.0) / 64.0});
-        const double t_tile = k_chunks * t_chunk + 800.0 * ((nbe + 3) / 4) + 500.0;
+        const double t_tile = k_chunks * t_chunk + 350.0 * ((nbe + 3) / 4) + 800.0;
         const double cost = per_cta * t_tile + 3000.0;
         if (best_nb == 0 || cost < best * 0.999) { best = cost; best_nb = nbe; }
     }
@@ -503,6 +557,7 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     w->K = K; w->N = N; w->ntile = ntile; w->size_hint = size_hint;
     const double density = (double)ntile / std::max(1.0, (double)NBR * (K / 16));
     w->nb = choose_nb(NBR, (K + kKC - 1) / kKC, size_hint, density);
+    if (nb_override <= 0 && g_tune[0] > 0) nb_override = g_tune[0];
     if (nb_override > 0) {
         const int nbo = std::min(nb_override, kMaxNB);
         w->nb = NBR <= nbo ? NBR : std::max(4, nbo / 4 * 4);
@@ -565,9 +620,9 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     w->stage_b_bytes = (int)((max_block + 1023) / 1024 * 1024);
     {
         const RingShape rs = ring_shape(w->nb, w->stage_b_bytes);
-        w->slots = rs.stages; w->a_slots = rs.a_slots; w->panel_bufs = rs.panel_bufs;
+        w->stages = rs.stages; w->a_slots = rs.a_slots; w->epi_bufs = rs.epi_bufs;
     }
-    if (w->slots < 2) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
+    if (w->stages < 2 || w->a_slots < 1) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
     w->stream_bytes = stream.size();
 
     cudaError_t e1 = cudaMalloc(&w->d_dir, dir.size() * sizeof(uint2));
@@ -616,6 +671,9 @@ int tile_weight_set_bias_device(TileWeight* w, const half* bias_dev, cudaStream_
     return cuda_status(cudaMemcpyAsync(w->d_bias, bias_dev, (size_t)w->N * sizeof(half), cudaMemcpyDeviceToDevice, st), "bias copy");
 }
 
+void tile_gemm_set_tuning(int nb, int x_stages, int b_stages, int epi_bufs) {
+    g_tune[0] = nb; g_tune[1] = x_stages; g_tune[2] = b_stages; g_tune[3] = epi_bufs;
+}
 static long long* g_prof = nullptr;
 void tile_gemm_set_profile_buffer(long long* dev_buf) { g_prof = dev_buf; }
 
@@ -626,12 +684,14 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     if (!aligned16(X) || !aligned16(Y)) return fail(ET_ERR_INVALID, "tile linear: X and Y must be 16-byte aligned");
     CUtensorMap tm, tmy;
     if (!make_tmap_panels_f16(&tm, X, (uint64_t)T, (uint64_t)w->K, (uint64_t)w->K, kSlab, kKC / kPanel) ||
-        !make_tmap_2d_f16(&tmy, Y, (uint64_t)T, (uint64_t)w->N, (uint64_t)w->N, kSlab, kPanel, true))
+        !make_tmap_2d_f16(&tmy, Y, (uint64_t)T, (uint64_t)w->N, (uint64_t)w->N, 32, kUnitCols, 64))
         return fail(ET_ERR_CUDA, "tile linear: cuTensorMapEncodeTiled failed");
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(tile_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        attr_err = cudaFuncSetAttribute(tile_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        if (attr_err == cudaSuccess)
+            attr_err = cudaFuncSetAttribute(tile_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
     });
     if (attr_err != cudaSuccess) return cuda_status(attr_err, "tile linear: shared memory opt-in");
     GemmParams p;
@@ -639,12 +699,14 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     p.T = T; p.N = w->N; p.k_chunks = w->k_chunks; p.nb = w->nb;
     p.n_chunks = w->n_chunks;
     p.n_tiles = ((T + kSlab - 1) / kSlab) * w->n_chunks;
-    p.stage_b_bytes = w->stage_b_bytes; p.slots = w->slots; p.a_slots = w->a_slots; p.panel_bufs = w->panel_bufs; p.gelu = gelu; p.err = w->d_err;
+    p.stage_b_bytes = w->stage_b_bytes; p.stages = w->stages; p.a_slots = w->a_slots; p.epi_bufs = w->epi_bufs; p.gelu = gelu; p.err = w->d_err;
     p.prof = g_prof;
     for (size_t c = 0; c < w->h_first.size(); ++c) p.first[c] = w->h_first[c];
-    const size_t smem = (size_t)w->slots * (kXStageBytes + w->stage_b_bytes) + (size_t)w->panel_bufs * kPanelBytes + sizeof(Shared) + 1024;
+    const size_t smem = (size_t)w->stages * (kXStageBytes + w->stage_b_bytes) +
+                        (size_t)w->epi_bufs * kIssuers * kUnitBytes + sizeof(Shared) + 1024;
     dim3 grid(std::min(p.n_tiles, sm_count()));
-    const cudaError_t le = launch_pdl(tile_gemm_kernel, grid, dim3(kThreads), smem, st, tm, tmy, p);
+    const cudaError_t le = gelu ? launch_pdl(tile_gemm_kernel<true>, grid, dim3(kThreads), smem, st, tm, tmy, p)
+                                : launch_pdl(tile_gemm_kernel<false>, grid, dim3(kThreads), smem, st, tm, tmy, p);
     if (le != cudaSuccess) return cuda_status(le, "tile linear launch");
     return cuda_status(cudaGetLastError(), "tile linear launch");
 }
@@ -661,7 +723,7 @@ int tile_weight_error(const TileWeight* w, int* code) {
 }
 
 void tile_weight_info(const TileWeight* w, int* info) {
-    info[0] = w->nb; info[1] = w->n_chunks; info[2] = w->k_chunks; info[3] = w->slots;
+    info[0] = w->nb; info[1] = w->n_chunks; info[2] = w->k_chunks; info[3] = w->stages;
     info[4] = w->stage_b_bytes; info[5] = (int)std::min<size_t>(w->stream_bytes, 0x7fffffff);
 }
 

@@ -26,10 +26,11 @@ inline EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D fp16 row-major tensor [rows x cols] with row pitch `pitch_elems`; box = box_rows x box_cols.
-// swizzle128: box_cols must be 64 (128 bytes). Out-of-range elements read as zero.
+// swizzle_bytes: 0 (none), 64 (box_cols must be 32) or 128 (box_cols must be 64). Out-of-range elements
+// read as zero and are not written.
 inline bool make_tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols,
                              uint64_t pitch_elems, uint32_t box_rows, uint32_t box_cols,
-                             bool swizzle128) {
+                             int swizzle_bytes) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     cuuint64_t dims[2] = {cols, rows};
@@ -38,7 +39,8 @@ inline bool make_tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, 
     cuuint32_t estr[2] = {1, 1};
     return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box,
               estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+              swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+              : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
