@@ -1,7 +1,10 @@
 #!/usr/bin/env python
 """One kernel at a time on inputs larger than L2: prints the achieved rate from CUDA events.
 
-    python et_b200/examples/kernel_cases.py {gemm|attention|attention512|layernorm|softmax} [launches]
+    python et_b200/examples/kernel_cases.py {gemm|attention|attention512|attention_mma|layernorm|softmax} [launches]
+
+`attention_mma` is `attention` with the lengths given only on the device, which the tcgen05 kernel declines
+(it needs the longest length on the host), so the mma.sync kernel runs.
 
 Sized for profiling too (a few hundred MB on the device, a handful of launches):
     ncu --set full --clock-control none -k regex:<kernel> -s 3 -c 2 -o out python et_b200/examples/kernel_cases.py gemm
@@ -45,12 +48,16 @@ def main():
         flops = 2.0 * T * 256 * len(ro)
         print(f"tile GEMM T={T} K={K} N={N} kept tiles {len(ro)} ({len(ro) / (N // 16 * K // 16):.3f}): {s * 1e6:.1f} us, "
               f"{flops / s / 1e12:.1f} TFLOP/s on kept tiles, {flops / s / 1e12 / (len(ro) / (N // 16 * K // 16)):.0f} dense-equivalent; {w.info()}")
-    elif case in ("attention", "attention512"):
+    elif case in ("attention", "attention512", "attention_mma"):
         S = 512 if case == "attention512" else 128
         B, d, H = (64, 768, 12) if S == 512 else (256, 768, 12)
         q, k, v = (torch.randn((B * S, d), device="cuda").half() for _ in range(3))
         o = torch.zeros_like(q)
-        s = timed(lambda: et.attention_batch(o, q, k, v, d, H, batch=B, uniform_len=S), n)
+        if case == "attention_mma":
+            cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device="cuda")
+            s = timed(lambda: et.attention_batch(o, q, k, v, d, H, cu_seqlens=cu, batch=B), n)
+        else:
+            s = timed(lambda: et.attention_batch(o, q, k, v, d, H, batch=B, uniform_len=S), n)
         flops = 4.0 * S * S * d * B
         print(f"attention B={B} S={S} d={d} H={H}: {s * 1e6:.1f} us, {flops / s / 1e12:.1f} TFLOP/s")
     elif case == "layernorm":
