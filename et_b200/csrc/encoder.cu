@@ -227,6 +227,57 @@ static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch,
     return et_skip_layernorm(out, b0, e->d_ln[2], e->d_ln[3], T, e->d_model, st);
 }
 
+
+// ------------------------------------------------------------------------------ stack of layers
+// N encoder layers run back to back on packed tokens: the caller's side of the reference's one-layer objects
+// (test/tile_test.cu:36-41 calls run() once for one layer). The model owns its scratch (grown on demand, kept
+// between calls), uploads the lengths once per call, and replays all N x 7 launches as one CUDA graph.
+struct Model {
+    std::vector<Encoder*> layers;
+    half* scratch = nullptr; size_t scratch_halfs = 0;
+    int* d_lens = nullptr; int lens_cap = 0;
+    struct Replay {
+        std::vector<int64_t> key;
+        int seen = 0;
+        cudaGraphExec_t exec = nullptr;
+    };
+    std::vector<Replay> replays;
+    bool use_graphs = true;
+    void drop_replays() {
+        for (auto& r : replays)
+            if (r.exec) cudaGraphExecDestroy(r.exec);
+        replays.clear();
+    }
+    ~Model() {
+        drop_replays();
+        for (auto* e : layers) delete e;
+        cudaFree(scratch);
+        cudaFree(d_lens);
+    }
+};
+
+static size_t model_scratch_halfs(const Model* m, int total_tokens, int batch, int max_len) {
+    size_t need = 0;
+    for (const Encoder* e : m->layers) {
+        size_t n = (size_t)5 * e->d_model * total_tokens;
+        if (e->kind == kLength && e->materialize_scores) n += (size_t)batch * e->nheads * max_len * max_len;
+        need = std::max(need, n);
+    }
+    return need;
+}
+
+static int model_forward(Model* m, half* out, const half* in, int T, const int* cu, const int* vl, int batch,
+                         int uniform_len, cudaStream_t st, int max_len) {
+    const half* x = in;
+    for (Encoder* e : m->layers) {
+        // a layer may write over its own input (the input is consumed before the last two launches write `out`)
+        const int rc = encoder_forward(e, out, x, m->scratch, T, cu, vl, batch, uniform_len, st, max_len);
+        if (rc) return rc;
+        x = out;
+    }
+    return ET_OK;
+}
+
 }  // namespace et
 
 using et::Encoder;
@@ -552,6 +603,154 @@ int et_encoder_set_graph_replay(et_encoder* enc, int on) {
     ET_REQUIRE(enc && enc->e, "et_encoder_set_graph_replay: null encoder");
     enc->e->use_graphs = on != 0;
     return ET_OK;
+}
+
+
+struct et_model {
+    et::Model* m;
+};
+
+int et_model_create(et_model** out, et_encoder* const* layers, int n_layers) {
+    ET_REQUIRE(out, "et_model_create: null output");
+    *out = nullptr;
+    ET_REQUIRE(layers && n_layers > 0, "et_model_create: no layers");
+    for (int i = 0; i < n_layers; ++i) {
+        ET_REQUIRE(layers[i] && layers[i]->e, "et_model_create: null or already consumed layer");
+        ET_REQUIRE(layers[i]->e->d_model == layers[0]->e->d_model, "et_model_create: layers differ in d_model");
+        for (int j = 0; j < i; ++j) ET_REQUIRE(layers[i] != layers[j], "et_model_create: the same layer twice");
+    }
+    auto* m = new et::Model();
+    for (int i = 0; i < n_layers; ++i) {
+        m->layers.push_back(layers[i]->e);
+        layers[i]->e = nullptr;   // ownership moves to the model; the caller still destroys the emptied handles
+    }
+    *out = new et_model{m};
+    return ET_OK;
+}
+
+int et_model_destroy(et_model* model) {
+    if (model) { delete model->m; delete model; }
+    return ET_OK;
+}
+
+int et_model_num_layers(const et_model* model) { return model && model->m ? (int)model->m->layers.size() : 0; }
+
+int et_model_set_graph_replay(et_model* model, int on) {
+    ET_REQUIRE(model && model->m, "et_model_set_graph_replay: null model");
+    model->m->use_graphs = on != 0;
+    return ET_OK;
+}
+
+// Grows the model's scratch to hold a batch of `total_tokens` packed tokens (and, for length layers that
+// materialise scores, batch x heads x max_len^2 scores). Graphs recorded with the old scratch are dropped.
+int et_model_reserve(et_model* model, int total_tokens, int batch, int max_len) {
+    ET_REQUIRE(model && model->m, "et_model_reserve: null model");
+    ET_REQUIRE(total_tokens >= 0 && batch >= 0 && max_len >= 0, "et_model_reserve: negative size");
+    et::Model* m = model->m;
+    const size_t need = et::model_scratch_halfs(m, total_tokens, batch, max_len);
+    if (need <= m->scratch_halfs) return ET_OK;
+    m->drop_replays();
+    cudaFree(m->scratch);
+    m->scratch = nullptr; m->scratch_halfs = 0;
+    if (cudaMalloc(&m->scratch, need * sizeof(half)) != cudaSuccess) return et::fail(ET_ERR_CUDA, "et_model_reserve: cudaMalloc failed");
+    m->scratch_halfs = need;
+    return ET_OK;
+}
+
+int et_model_run_batch(et_model* model, void* out, const void* in, const int* seq_lens_host,
+                       const int* valid_lens_host, int batch, void* stream) {
+    ET_REQUIRE(model && model->m && out && in, "et_model_run_batch: null pointer");
+    ET_REQUIRE(batch >= 0, "et_model_run_batch: negative batch");
+    et::Model* m = model->m;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (batch == 0) return ET_OK;
+    ET_REQUIRE(seq_lens_host, "et_model_run_batch: null seq_lens");
+    std::vector<int> meta(2 * batch + 1);
+    meta[0] = 0;
+    bool uniform = true;
+    int max_len = 0;
+    for (int b = 0; b < batch; ++b) {
+        ET_REQUIRE(seq_lens_host[b] >= 0, "et_model_run_batch: negative sequence length");
+        for (Encoder* e : m->layers)
+            ET_REQUIRE(!e->d_mask || seq_lens_host[b] <= e->seq_len, "et_model_run_batch: sequence longer than a layer's mask");
+        meta[b + 1] = meta[b] + seq_lens_host[b];
+        meta[batch + 1 + b] = valid_lens_host ? valid_lens_host[b] : seq_lens_host[b];
+        uniform = uniform && seq_lens_host[b] == seq_lens_host[0];
+        max_len = std::max(max_len, seq_lens_host[b]);
+    }
+    const int T = meta[batch];
+    if (T == 0) return ET_OK;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    const bool capturing = cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone;
+    if (capturing) {
+        // inside the caller's own capture nothing may be allocated or uploaded from a temporary
+        ET_REQUIRE(et::model_scratch_halfs(m, T, batch, max_len) <= m->scratch_halfs,
+                   "et_model_run_batch: call et_model_reserve before capturing");
+        ET_REQUIRE(uniform && !valid_lens_host, "et_model_run_batch: only equal-length batches can run inside the caller's capture");
+    } else {
+        int rc = et_model_reserve(model, T, batch, max_len);
+        if (rc) return rc;
+    }
+    const int* cu = nullptr;
+    const int* vl = nullptr;
+    if (!uniform || valid_lens_host) {
+        if (m->lens_cap < 2 * batch + 1) {
+            cudaFree(m->d_lens);
+            m->d_lens = nullptr;
+            if (cudaMalloc(&m->d_lens, sizeof(int) * (2 * batch + 1)) != cudaSuccess)
+                return et::fail(ET_ERR_CUDA, "et_model_run_batch: cudaMalloc failed");
+            m->lens_cap = 2 * batch + 1;
+        }
+        int rc = et::cuda_status(cudaMemcpyAsync(m->d_lens, meta.data(), sizeof(int) * (2 * batch + 1),
+                                                 cudaMemcpyHostToDevice, st), "et_model_run_batch: lengths upload");
+        if (rc) return rc;
+        if (!uniform) cu = m->d_lens;
+        if (valid_lens_host) vl = m->d_lens + batch + 1;
+    }
+    half* o = static_cast<half*>(out);
+    const half* x = static_cast<const half*>(in);
+    const int ul = uniform ? seq_lens_host[0] : 0;
+    if (!m->use_graphs || capturing) return et::model_forward(m, o, x, T, cu, vl, batch, ul, st, max_len);
+    // First call with given buffers and lengths runs directly, the second is captured, later ones replay.
+    std::vector<int64_t> key = {(int64_t)(intptr_t)out, (int64_t)(intptr_t)in, (int64_t)batch,
+                                (int64_t)(valid_lens_host != nullptr)};
+    for (Encoder* e : m->layers) key.push_back((int64_t)e->materialize_scores);
+    for (int v : meta) key.push_back(v);
+    et::Model::Replay* slot = nullptr;
+    for (auto& r : m->replays)
+        if (r.key == key) slot = &r;
+    if (!slot) {
+        if (m->replays.size() >= 8) {
+            if (m->replays.front().exec) cudaGraphExecDestroy(m->replays.front().exec);
+            m->replays.erase(m->replays.begin());
+        }
+        m->replays.push_back({key, 0, nullptr});
+        slot = &m->replays.back();
+    }
+    if (slot->exec) return et::cuda_status(cudaGraphLaunch(slot->exec, st), "et_model_run_batch: graph launch");
+    if (slot->seen++ == 0) return et::model_forward(m, o, x, T, cu, vl, batch, ul, st, max_len);
+    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        return et::model_forward(m, o, x, T, cu, vl, batch, ul, st, max_len);
+    }
+    const int frc = et::model_forward(m, o, x, T, cu, vl, batch, ul, st, max_len);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(st, &graph);
+    if (frc != ET_OK || ce != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        m->use_graphs = false;   // plain launches from now on
+        return et::model_forward(m, o, x, T, cu, vl, batch, ul, st, max_len);
+    }
+    const cudaError_t ie = cudaGraphInstantiate(&slot->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+        slot->exec = nullptr;
+        cudaGetLastError();
+        m->use_graphs = false;
+        return et::model_forward(m, o, x, T, cu, vl, batch, ul, st, max_len);
+    }
+    return et::cuda_status(cudaGraphLaunch(slot->exec, st), "et_model_run_batch: graph launch");
 }
 
 }  // extern "C"

@@ -14,6 +14,7 @@ __all__ = [
     "RowWeight", "attention_otf", "attention_prune", "qk_scores", "attention_sharedqk", "attention_batch", "attention_static_scores",
     "gen_sparse_tile_mat", "gen_sparse_row_mat", "build_head_ptr", "Encoder", "encoder_buffer_size",
     "encoder_batch_buffer_size", "KIND_TILE", "KIND_PRUNE", "KIND_LENGTH", "KIND_PRUNE_QKV",
+    "Model", "prune_dense_to_tiles", "select_rows_magnitude", "compact_rows",
 ]
 
 _i = ctypes.c_int
@@ -273,3 +274,82 @@ class Encoder:
             self.close()
         except Exception:
             pass
+
+
+class Model:
+    """A stack of encoder layers run back to back on packed tokens (et_model_* of the C ABI). Takes ownership of
+    the layers of the `Encoder` objects given (they become empty shells). Scratch is owned by the model."""
+
+    def __init__(self, encoders):
+        self._encoders = list(encoders)
+        arr = (ctypes.c_void_p * len(self._encoders))(*[e._h for e in self._encoders])
+        self._h = ctypes.c_void_p(0)
+        check(lib().et_model_create(ctypes.byref(self._h), arr, _i(len(self._encoders))))
+
+    @property
+    def num_layers(self):
+        return int(lib().et_model_num_layers(self._h))
+
+    def reserve(self, total_tokens, batch, max_len):
+        check(lib().et_model_reserve(self._h, _i(total_tokens), _i(batch), _i(max_len)))
+
+    def run_batch(self, out, x, seq_lens, valid_lens=None, stream=None):
+        seq_lens = np.ascontiguousarray(seq_lens, dtype=np.int32)
+        valid = None if valid_lens is None else np.ascontiguousarray(valid_lens, dtype=np.int32)
+        check(lib().et_model_run_batch(self._h, ptr(out), ptr(x), ptr(seq_lens), ptr(valid), _i(len(seq_lens)),
+                                       stream_ptr(stream)))
+        return out
+
+    def set_graph_replay(self, on):
+        check(lib().et_model_set_graph_replay(self._h, _i(1 if on else 0)))
+
+    def close(self):
+        if self._h:
+            lib().et_model_destroy(self._h)
+            self._h = ctypes.c_void_p(0)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---------------------------------------------------------------------------------- real-weight ingestion
+def prune_dense_to_tiles(weight, sparsity):
+    """Dense fp16 [out_feat, in_feat] -> (row_ptr, row_offset, data[ntile, 256]) keeping the tiles of largest norm."""
+    w = np.ascontiguousarray(weight, dtype=np.float16)
+    out_feat, in_feat = w.shape
+    cap = (out_feat // 16) * (in_feat // 16)
+    row_ptr = np.zeros(out_feat // 16 + 1, dtype=np.int32)
+    row_offset = np.zeros(max(cap, 1), dtype=np.int32)
+    data = np.zeros((max(cap, 1), 256), dtype=np.float16)
+    n = _i(0)
+    check(lib().et_prune_dense_to_tiles(ptr(w), _i(out_feat), _i(in_feat), ctypes.c_float(sparsity), ptr(row_ptr),
+                                        ptr(row_offset), ptr(data), _i(cap), ctypes.byref(n)))
+    return row_ptr, row_offset[:n.value].copy(), data[:n.value].copy()
+
+
+def select_rows_magnitude(weights, nhead, sparsity):
+    """Row ids (ascending) kept per head by summed squared norm over the given dense [out_feat, in_feat] weights."""
+    ws = [np.ascontiguousarray(w, dtype=np.float16) for w in weights]
+    out_feat, in_feat = ws[0].shape
+    arr = (ctypes.c_void_p * len(ws))(*[w.ctypes.data for w in ws])
+    row_id = np.zeros(out_feat, dtype=np.int32)
+    n = _i(0)
+    check(lib().et_select_rows_magnitude(arr, _i(len(ws)), _i(out_feat), _i(in_feat), _i(nhead),
+                                         ctypes.c_float(sparsity), ptr(row_id), _i(out_feat), ctypes.byref(n)))
+    return row_id[:n.value].copy()
+
+
+def compact_rows(weight, bias, row_id):
+    """(weight[ceil16(n), in_feat], bias[ceil16(n)]) of the kept rows, zero padded."""
+    w = np.ascontiguousarray(weight, dtype=np.float16)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float16)
+    row_id = np.ascontiguousarray(row_id, dtype=np.int32)
+    nrow = (len(row_id) + 15) // 16 * 16
+    wc = np.zeros((nrow, w.shape[1]), dtype=np.float16)
+    bc = np.zeros(nrow, dtype=np.float16)
+    check(lib().et_compact_rows(ptr(w), ptr(b), _i(w.shape[0]), _i(w.shape[1]), ptr(row_id), _i(len(row_id)),
+                                ptr(wc), ptr(bc)))
+    return wc, bc

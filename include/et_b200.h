@@ -144,6 +144,24 @@ int et_gen_sparse_tile_mat(int nrow, int ncol, float sparsity, uint64_t seed, in
 int et_gen_sparse_row_mat(int nrow, float sparsity, uint64_t seed, int nhead, int* row_id, int cap, int* nkeep);
 int et_build_head_ptr(const int* row_id, int n, int nhead, int out_feat, int* head_ptr);
 
+/* ---- real-weight ingestion (host; extension) ------------------------------------------------------
+ * The reference only draws random structure (test/tile_mat.cu, test/row_mat.cu) and defines no on-disk format.
+ * These turn a dense fp16 weight [out_feat x in_feat] (row-major) into exactly the arrays Linear_tile
+ * (encoder/Linear.h:18-24) and Linear_row (encoder/Linear.h:66-67) take, by magnitude; ties keep the lower
+ * index, so the result is a pure function of the weight.
+ * et_prune_dense_to_tiles: keeps the floor(total*(1-sparsity)) 16x16 tiles of largest sum of squares; tiles of a
+ *   block-row in ascending column order; data[i*256 + n*16 + k] = W[16r+n, row_offset[i]+k].
+ * et_select_rows_magnitude: per head keeps the round(head_dim*(1-sparsity)) (at least 1) rows of largest sum of
+ *   squares, summed over the n_mats matrices given (pass Q and K together so that they retain the same
+ *   dimensions); row_id ascending.
+ * et_compact_rows: weight_compact [ceil16(nkeep) x in_feat] (zero rows as padding), bias_compact [ceil16(nkeep)]. */
+int et_prune_dense_to_tiles(const void* dense_host, int out_feat, int in_feat, float sparsity, int* row_ptr,
+                            int* row_offset, void* data, int cap_tiles, int* ntile);
+int et_select_rows_magnitude(const void* const* dense_hosts, int n_mats, int out_feat, int in_feat, int nhead,
+                             float sparsity, int* row_id, int cap, int* nkeep);
+int et_compact_rows(const void* dense_host, const void* bias_host, int out_feat, int in_feat, const int* row_id,
+                    int nkeep, void* weight_compact, void* bias_compact);
+
 /* ---- encoder layers ----------------------------------------------------------------------------
  * One post-LN encoder layer: Q,K,V linears -> attention -> output linear -> add+LayerNorm -> MLP1 (GELU)
  * -> MLP2 -> add+LayerNorm (encoder/encoder.cu:20-45). LayerNorm vectors (d_model) and mask
@@ -189,6 +207,21 @@ int et_encoder_set_graph_replay(et_encoder* enc, int on);
 /* Length encoder only: route attention through scores materialised in HBM (the reference's structure,
  * encoder/encoder.cu:126-136) instead of the default on-the-fly kernel. Equal-length batches only. */
 int et_encoder_set_materialize_scores(et_encoder* enc, int on);
+
+/* ---- Stack of encoder layers (extension: no counterpart in the reference, whose objects hold one layer and
+ * whose callers run it once, test/tile_test.cu:36-41). The model takes ownership of the layers (the caller still
+ * calls et_encoder_destroy on the emptied handles), owns its scratch (et_model_reserve, or grown on demand by
+ * et_model_run_batch outside stream capture), and from the third call with the same buffers and lengths replays
+ * all launches of all layers as one CUDA graph. `out` may alias `in`. Layers may be of different kinds; they
+ * must agree in d_model. */
+typedef struct et_model et_model;
+int et_model_create(et_model** out, et_encoder* const* layers, int n_layers);
+int et_model_destroy(et_model* model);
+int et_model_num_layers(const et_model* model);
+int et_model_reserve(et_model* model, int total_tokens, int batch, int max_len);
+int et_model_run_batch(et_model* model, void* out, const void* in, const int* seq_lens_host,
+                       const int* valid_lens_host, int batch, void* stream);
+int et_model_set_graph_replay(et_model* model, int on);
 
 #ifdef __cplusplus
 }

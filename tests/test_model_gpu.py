@@ -1,0 +1,116 @@
+"""GPU tests of the layer stack (et_model_*) and of ingested real weights: a stack equals its layers run one by
+one (bit-exact) and the oracle's layers chained (tolerance); magnitude-pruned weights give the masked-dense result."""
+import numpy as np
+import pytest
+
+from tests import util
+from tests.test_encoder_gpu import build_encoder, dev, host, make_layer, orc_lin
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def et():
+    import et_b200
+    et_b200.lib()
+    return et_b200
+
+
+def test_model_equals_layers_one_by_one_and_oracle(et, orc):
+    d, H, dff, n_layers = 256, 4, 1024, 3
+    lens = [50, 128, 17, 96]
+    T = sum(lens)
+    layers = [make_layer(orc, d, dff, 0.5, seed=20 + 7 * i) for i in range(n_layers)]
+    X = util.activations(31, (T, d))
+    # oracle: layers chained in fp32 with fp16 storage between layers (what the GPU path stores)
+    want = X
+    for lin, ln in layers:
+        want = orc.encoder_layer(np.asarray(want, dtype=np.float16), orc_lin(lin), ln, lens, d, H).astype(np.float16)
+    # layers one by one through the single-layer object
+    singles = [build_encoder(et, et.KIND_TILE, lin, ln, d, 128, H, T) for lin, ln in layers]
+    scratch = torch.zeros(et.encoder_batch_buffer_size(et.KIND_TILE, d, T, len(lens), 128, H) // 2,
+                          dtype=torch.float16, device="cuda")
+    x = dev(X)
+    step = torch.zeros_like(x)
+    cur = x
+    for enc in singles:
+        enc.run_batch(step, cur, lens, scratch)
+        cur = step.clone()
+    torch.cuda.synchronize()
+    # the stack: direct run, captured run, replayed run must all agree bit for bit with the chain
+    model = et.Model([build_encoder(et, et.KIND_TILE, lin, ln, d, 128, H, T) for lin, ln in layers])
+    assert model.num_layers == n_layers
+    out = torch.zeros_like(x)
+    for call in range(4):
+        out.zero_()
+        model.run_batch(out, x, lens)
+        torch.cuda.synchronize()
+        assert torch.equal(out, cur), f"call {call}"
+    util.assert_close(host(out), want.astype(np.float32), max_abs=4e-2, mean_abs=4e-3, what="3-layer stack vs oracle")
+    # in place, equal lengths, no graphs
+    model.set_graph_replay(False)
+    xe = dev(util.activations(32, (3 * 64, d)))
+    ref = torch.zeros_like(xe)
+    model.run_batch(ref, xe, [64] * 3)
+    model.run_batch(xe, xe, [64] * 3)
+    torch.cuda.synchronize()
+    assert torch.equal(xe, ref)
+
+
+def test_model_argument_checks(et, orc):
+    d, H, dff = 128, 2, 256
+    lin, ln = make_layer(orc, d, dff, 0.5, seed=40)
+    enc = build_encoder(et, et.KIND_TILE, lin, ln, d, 64, H, 64)
+    lin2, ln2 = make_layer(orc, 256, 512, 0.5, seed=41)
+    other = build_encoder(et, et.KIND_TILE, lin2, ln2, 256, 64, 4, 64)
+    with pytest.raises(et.EtError):
+        et.Model([enc, other])          # d_model differs
+    with pytest.raises(et.EtError):
+        et.Model([enc, enc])            # the same layer twice
+    model = et.Model([enc])
+    with pytest.raises(et.EtError):
+        et.Model([enc])                 # already consumed
+    x = torch.zeros((64, d), dtype=torch.float16, device="cuda")
+    with pytest.raises(et.EtError):
+        model.run_batch(x, x, [-1])
+    model.run_batch(x, x, [])           # empty batch is a no-op
+
+
+def test_ingested_tiles_give_the_masked_dense_product(et, orc):
+    rng = np.random.default_rng(11)
+    K, N, T = 256, 384, 200
+    W = (rng.standard_normal((N, K)) * 0.05).astype(np.float16)
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float16)
+    rp, ro, data = et.prune_dense_to_tiles(W, 0.6)
+    w = et.TileWeight(K, N, T, data, rp, ro, bias)
+    X = util.activations(12, (T, K))
+    y = torch.zeros((T, N), dtype=torch.float16, device="cuda")
+    w.run(y, dev(X))
+    torch.cuda.synchronize()
+    masked = np.zeros((N, K), np.float32)
+    for r in range(N // 16):
+        for t in range(rp[r], rp[r + 1]):
+            masked[r * 16:(r + 1) * 16, ro[t]:ro[t] + 16] = W[r * 16:(r + 1) * 16, ro[t]:ro[t] + 16]
+    want = X.astype(np.float32) @ masked.T + bias.astype(np.float32)
+    util.assert_close(host(y), want, what="ingested tile weight")
+    # dropped tiles are the smallest ones
+    kept = int((N // 16) * (K // 16) * 0.4)
+    assert len(ro) == kept
+
+
+def test_ingested_rows_through_row_linear(et, orc):
+    rng = np.random.default_rng(13)
+    K, N, H, T = 128, 256, 4, 96
+    W = (rng.standard_normal((N, K)) * 0.05).astype(np.float16)
+    bias = (rng.standard_normal(N) * 0.1).astype(np.float16)
+    ids = et.select_rows_magnitude([W], H, 0.5)
+    wc, bc = et.compact_rows(W, bias, ids)
+    rw = et.RowWeight(K, N, T, wc, ids, bc, H)
+    X = util.activations(14, (T, K))
+    y = torch.zeros((T, rw.nrow), dtype=torch.float16, device="cuda")
+    rw.run(y, dev(X))
+    torch.cuda.synchronize()
+    want = X.astype(np.float32) @ W[ids].astype(np.float32).T + bias[ids].astype(np.float32)
+    util.assert_close(host(y)[:, :len(ids)], want, what="ingested row weight")
+    assert rw.head_ptr.tolist() == et.build_head_ptr(ids, H, N).tolist()
