@@ -93,6 +93,17 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def set_shape(args):
+    """Other shapes of the same tile-pruned layer (e.g. --batch 1 --sparsity 0 for the dense single-sequence case,
+    --batch 32 --seq 512 --d-model 1024 --heads 16 --ff 4096 --sparsity 0.8 for a BERT-large shard). The instance
+    count shrinks with the size of an instance but the instances together always exceed L2."""
+    global D_MODEL, NHEAD, D_FF, BATCH, SEQ, T, INSTANCES
+    D_MODEL, NHEAD, D_FF, BATCH, SEQ = args.d_model, args.heads, args.ff, args.batch, args.seq
+    T = BATCH * SEQ
+    per_instance = 7 * T * D_MODEL * 2 + (4 * D_MODEL * D_MODEL + 2 * D_MODEL * D_FF) * 2 * (1.0 - args.sparsity)
+    INSTANCES = int(max(2, min(12, -(-300e6 // per_instance))))
+
+
 def make_layer_host(orc, sparsity, seed):
     from tests import util
     shapes = {"q": (D_MODEL, D_MODEL), "k": (D_MODEL, D_MODEL), "v": (D_MODEL, D_MODEL), "o": (D_MODEL, D_MODEL),
@@ -127,12 +138,15 @@ def cpu_baseline(orc, lin, ln, X):
 
 
 def workload_config(args):
-    return {"workload": f"config 2 (encoder_tile_test): one tile-pruned BERT-base encoder layer, batch {BATCH} x seq {SEQ}, "
+    name = "config 2 (encoder_tile_test)" if (D_MODEL, NHEAD, D_FF, BATCH, SEQ) == (768, 12, 3072, 16, 128) else "encoder_tile_test shape"
+    return {"workload": f"{name}: one tile-pruned BERT encoder layer, batch {BATCH} x seq {SEQ}, "
                         f"hidden {D_MODEL}, {NHEAD} heads, FFN {D_FF}, Bernoulli 16x16 tile sparsity {args.sparsity} per GPU",
             "global_batch": BATCH * args.gpus, "seq_len": SEQ, "sparsity": args.sparsity,
             "parallelism": f"dp{args.gpus}" if args.gpus > 1 else "single",
+            "gather": (f"NCCL all-gather of the output shards, the outputs of {args.gather_every} consecutive steps per collective, "
+                       "asynchronous, joined inside the timed region") if args.gpus > 1 else "none",
             "l2": f"inputs larger than L2: {INSTANCES} independent instances of the layer (weights, activations, scratch, about "
-                  f"25 MB each) visited round-robin"}
+                  f"{7 * T * D_MODEL * 2 / 1e6:.0f} MB each) visited round-robin"}
 
 
 def timed(step, steps, finish=None):
@@ -163,12 +177,12 @@ def run_reference(args, rank):
             "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "config": workload_config(args)}
     ref = oracle_lib.load_ref()
-    cpu = cpu_baseline(orc, lin, ln, X)
     try:
         import torch
         have_gpu = torch.cuda.is_available()
     except Exception:
         have_gpu = False
+    cpu = cpu_baseline(orc, lin, ln, X) if (ref is None or not have_gpu or not args.no_cpu_baseline) else None
     if ref is None or not have_gpu:
         base.update({"value": cpu["value"], "ms_per_step": 1e3 * BATCH / cpu["value"], "cpu_baseline": cpu,
                      "reference_kind": "fp32 CPU oracle (the reference ships no CPU path and its CUDA library is not built here)",
@@ -242,10 +256,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=3000)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--sparsity", type=float, default=0.75)
+    ap.add_argument("--batch", type=int, default=BATCH, help="sequences per GPU (other configurations of the tile layer)")
+    ap.add_argument("--seq", type=int, default=SEQ)
+    ap.add_argument("--d-model", type=int, default=D_MODEL)
+    ap.add_argument("--heads", type=int, default=NHEAD)
+    ap.add_argument("--ff", type=int, default=D_FF)
+    ap.add_argument("--gather-every", type=int, default=4,
+                    help="multi-GPU: output shards of this many steps travel in one all-gather (must divide the instance count)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the sweep and the LayerNorm/softmax bandwidth legs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    set_shape(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -267,18 +289,28 @@ def main():
     pk = peaks()
     orc = oracle_lib.load()
     lens = [SEQ] * BATCH
-    # output shards are gathered with one NCCL all-gather per step, issued asynchronously: the next step's layer
-    # does not wait for it (ring of 4 destination buffers, at most 2 collectives in flight, all joined before the
-    # closing event of a timed region)
-    gathered = [torch.zeros((world * T, D_MODEL), dtype=torch.float16, device="cuda") for _ in range(4)] if world > 1 else None
+    # Output shards are gathered over NVLink with NCCL all-gathers issued asynchronously: the next steps' layers do
+    # not wait for them. The outputs of GE consecutive steps land side by side in one of three staging buffers and
+    # travel in one collective (every output row is gathered inside the timed region; fewer, larger collectives
+    # take fewer SMs away from the layer's kernels). At most 2 collectives are in flight, all are joined before
+    # the closing event of a timed region.
+    GE = args.gather_every if world > 1 else 1
+    if world > 1 and (GE < 1 or INSTANCES % GE or (INSTANCES // GE) % 3):
+        GE = 1
+    stage = [torch.zeros((GE * T, D_MODEL), dtype=torch.float16, device="cuda") for _ in range(3)] if world > 1 else None
+    gathered = [torch.zeros((world * GE * T, D_MODEL), dtype=torch.float16, device="cuda") for _ in range(4)] if world > 1 else None
     pending = collections.deque()
+    open_group = [None]   # a group whose last step has not run yet
 
-    def gather(i, out):
-        pending.append(dist.all_gather_into_tensor(gathered[i % 4], out, async_op=True))
+    def gather(group):
+        pending.append(dist.all_gather_into_tensor(gathered[group % 4], stage[group % 3], async_op=True))
         if len(pending) > 2:
             pending.popleft().wait()
 
     def join():
+        if open_group[0] is not None:   # the step count was not a multiple of GE: gather the partial group too
+            gather(open_group[0])
+            open_group[0] = None
         while pending:
             pending.popleft().wait()
 
@@ -299,9 +331,17 @@ def main():
     def layer_step(insts):
         def step(i):
             it = insts[i % len(insts)]
-            it.enc.run_batch(it.out, it.x, lens, it.scratch)
             if world > 1:
-                gather(i, it.out)
+                # with GE dividing the instance count (and the quotient a multiple of 3) an instance always writes
+                # to the same slice, so its replayed graph stays valid
+                group, slot = divmod(i, GE)
+                it.enc.run_batch(stage[group % 3][slot * T:(slot + 1) * T], it.x, lens, it.scratch)
+                open_group[0] = group
+                if slot == GE - 1:
+                    gather(group)
+                    open_group[0] = None
+            else:
+                it.enc.run_batch(it.out, it.x, lens, it.scratch)
         return step
 
     def measure(insts, steps, warmup):
@@ -336,7 +376,7 @@ def main():
         it.x.copy_(hx[i % INSTANCES], non_blocking=True)
         it.enc.run_batch(it.out, it.x, lens, it.scratch)
         if world > 1:
-            dist.all_gather_into_tensor(gathered[0], it.out)
+            dist.all_gather_into_tensor(gathered[0][:world * T], it.out)
         ho[i % INSTANCES].copy_(it.out, non_blocking=True)
         torch.cuda.synchronize()          # the caller needs the result on the host before its next batch
     for i in range(INSTANCES):

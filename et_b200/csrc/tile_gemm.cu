@@ -302,7 +302,8 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 if (lane == 1) {
                     got = mbar_wait(&sh->full[bs], phb);
                     // the tensor-memory slot: the chunk a_slots before this one must be done
-                    if (got && it >= RA) {
+                    // (with as many slots as stages the producer has already waited for that chunk)
+                    if (got && RA < DB && it >= RA) {
                         const int prev = it - RA;
                         got = mbar_wait(&sh->done[prev % DB], (uint32_t)(prev / DB) & 1u);
                     }
@@ -518,7 +519,7 @@ static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double densi
     const int sms = std::max(1, sm_count());
     double best = 0;
     int best_nb = 0;
-    for (int nb : {24, 20, 16, 12, 8}) {
+    for (int nb : {24, 20, 16, 12, 8, 4}) {
         // chunks other than a single one must cover whole 64-column output panels (nb % 4 == 0)
         const int nbe = n_block_rows <= nb ? std::max(n_block_rows, 1) : nb;
         if (nbe > kMaxNB) continue;
