@@ -8,7 +8,9 @@
 //                      swizzle), fp32 S_j in 128 TMEM columns
 //   softmax            eight warps, two threads per query row (64 keys each): tcgen05.ld, scale (log2 domain),
 //                      additive mask, key validity, running max / sum in fp32, P_j = 2^(s - max) as packed fp16
-//                      into 64 more TMEM columns (tcgen05.st), O rescaled by 2^(old max - new max) in place
+//                      into 64 more TMEM columns (tcgen05.st), O rescaled by 2^(old max - new max) in place.
+//                      P has its own columns, so Q K_{j+1}^T is issued together with P_j V_j and the next
+//                      block's row maxima are computed while P_j V_j runs
 //   O += P_j V_j       TS UMMA 128x64x16 (x8): A = P_j read from tensor memory, B = V_j in shared memory as loaded
 //                      (rows = keys), used as an MN-major operand
 //   epilogue           O / row sum -> fp16 -> global, rows beyond the sequence are not written
@@ -29,9 +31,10 @@ constexpr int kBQ = 128, kBK = 128, kHD = 64;
 constexpr int kTile = kBQ * kHD * 2;      // 16 KB: one 128 x 64 fp16 tile
 constexpr int kSoftmaxWarps = 8;          // two threads per query row, each owns 64 of the 128 keys of a block
 constexpr int kThreads = 32 * (kSoftmaxWarps + 1);   // + 1 warp whose lane 0 issues TMA and UMMA
-constexpr int kTmemCols = 256;            // S/P 128 | O 64 | row sums 16: two CTAs share an SM's tensor memory
-constexpr uint32_t kOCol = 128, kSumCol = 192;
+constexpr int kTmemCols = 256;            // S 128 | P 64 | O 64: two CTAs share an SM's tensor memory
+constexpr uint32_t kPCol = 128, kOCol = 192;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleStep = 8.f;       // log2 units by which a row maximum must grow before O is rescaled
 
 struct TcParams {
     half* Z;
@@ -56,8 +59,7 @@ struct TcShared {
     uint32_t tmem_base;
     int seq[3];
     volatile int abort;
-    float xmax[2][kBQ];   // block maximum of each half-row, exchanged between the two threads of a row
-    __align__(16) half ones[256];   // a 16 x 16 B operand of ones: P . ones^T puts the row sums of P in 16 TMEM columns
+    float xmax[2][kBQ];   // block maximum (at the end: sum) of each half-row, exchanged between the two threads of a row
 };
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -81,6 +83,19 @@ __device__ __forceinline__ uint32_t ex2_h2(uint32_t x) {
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
     half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Sum of 32 packed fp16 values (each <= 1): two levels of packed adds (partial sums <= 4), then fp32. The row sum
+// is thereby the sum of exactly the fp16 P values that are multiplied with V.
+__device__ __forceinline__ float sum_packed(const uint32_t (&pk)[16]) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const half2* h2 = reinterpret_cast<const half2*>(pk) + 4 * i;
+        const float2 f = __half22float2(__hadd2(__hadd2(h2[0], h2[1]), __hadd2(h2[2], h2[3])));
+        s += f.x + f.y;
+    }
+    return s;
 }
 
 // The two warps that share a quarter of the rows (64 threads) meet on their own hardware barrier.
@@ -138,8 +153,6 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
         sh->abort = 0;
         fence_mbar_init();
     }
-    if (tid < 128) reinterpret_cast<uint32_t*>(sh->ones)[tid] = 0x3c003c00u;   // 1.0 | 1.0
-    fence_proxy_async_smem();
     if (warp == kSoftmaxWarps) {
         tmem_alloc(&sh->tmem_base, kTmemCols);
         tmem_relinquish();
@@ -176,40 +189,44 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
     if (b >= 0 && nkb > 0) {
         if (warp == kSoftmaxWarps) {
             if (lane == 0) {
-                auto load_kv = [&](int j) {
+                auto load_k = [&](int j) {
                     const int st = j & 1;
                     mbar_expect_tx(&sh->k_full[st], kTile);
                     tma_load_2d(sK + (size_t)st * kTile, &tmK, h * kHD, tok0 + j * kBK, &sh->k_full[st]);
+                };
+                auto load_v = [&](int j) {
+                    const int st = j & 1;
                     mbar_expect_tx(&sh->v_full[st], kTile);
                     tma_load_2d(sV + (size_t)st * kTile, &tmV, h * kHD, tok0 + j * kBK, &sh->v_full[st]);
                 };
                 mbar_expect_tx(&sh->q_full, kTile);
                 tma_load_2d(sQ, &tmQ, h * kHD, tok0 + q0, &sh->q_full);
-                load_kv(0);
-                if (nkb > 1) load_kv(1);
+                load_k(0);
+                load_v(0);
+                if (nkb > 1) { load_k(1); load_v(1); }
                 const uint32_t idesc_qk = make_idesc_f16(128, 128);
                 const uint32_t idesc_pv = make_idesc_f16(128, 64, false, true);   // V is an MN-major B operand
-                const uint32_t idesc_sum = make_idesc_f16(128, 16);
-                const uint64_t ones_desc = make_smem_desc(smem_u32(sh->ones), 128, 256, 0);
                 const uint32_t qa = smem_u32(sQ);
-                AT_STAMP(10);
-                bool ok = mbar_wait(&sh->q_full, 0);
-                AT_STAMP(11);
-                for (int j = 0; j < nkb && ok; ++j) {
-                    const int st = j & 1;
-                    const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-                    if (sh->abort) { ok = false; break; }
-                    // S = Q K_j^T (the S / P columns are free: P_{j-1} V_{j-1} has completed, see below)
-                    ok = mbar_wait(&sh->k_full[st], ph);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const uint32_t ka = smem_u32(sK + (size_t)st * kTile);
+                auto issue_qk = [&](int j) {   // S = Q K_j^T into the S columns
+                    const uint32_t ka = smem_u32(sK + (size_t)(j & 1) * kTile);
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks)
                         umma_f16(tmem, make_smem_desc(qa + ks * 32, 16, 1024, 2), make_smem_desc(ka + ks * 32, 16, 1024, 2),
                                  idesc_qk, ks > 0);
                     umma_commit(&sh->s_ready);
-                    if (j == 0) AT_STAMP(13);
+                };
+                AT_STAMP(10);
+                bool ok = mbar_wait(&sh->q_full, 0) && mbar_wait(&sh->k_full[0], 0);
+                AT_STAMP(11);
+                if (ok) {
+                    tc_fence_after();
+                    issue_qk(0);
+                    AT_STAMP(13);
+                }
+                for (int j = 0; j < nkb && ok; ++j) {
+                    const int st = j & 1;
+                    const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+                    if (sh->abort) { ok = false; break; }
                     // O += P_j V_j once the softmax warps have written P_j (and rescaled O)
                     ok = mbar_wait(&sh->p_ready, (uint32_t)j & 1u) && mbar_wait(&sh->v_full[st], ph);
                     if (!ok) break;
@@ -217,20 +234,25 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                     tc_fence_after();
                     const uint32_t va = smem_u32(sV + (size_t)st * kTile);
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        // P of keys 16ks..16ks+15: each half-row's P sits at the start of its own half of the S columns
-                        const uint32_t pa = tmem + (uint32_t)((ks >> 2) * 64 + (ks & 3) * 8);
-                        const uint32_t acc = (j > 0 || ks > 0) ? 1u : 0u;
-                        umma_f16_ts(tmem + kOCol, pa, make_smem_desc(va + ks * 2048, 0, 1024, 2), idesc_pv, acc);
-                        umma_f16_ts(tmem + kSumCol, pa, ones_desc, idesc_sum, acc);
-                    }
+                    for (int ks = 0; ks < 8; ++ks)   // P of keys 16ks..16ks+15: 8 packed columns
+                        umma_f16_ts(tmem + kOCol, tmem + kPCol + (uint32_t)(ks * 8), make_smem_desc(va + ks * 2048, 0, 1024, 2),
+                                    idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(&sh->pv_done);
                     AT_STAMP(15 + 2 * j);
                     if (j + 1 < nkb) {
-                        // the stage and the P columns are reused: wait until this block's UMMAs have finished
-                        ok = mbar_wait(&sh->pv_done, (uint32_t)j & 1u);
+                        // S_{j+1} right behind it: every softmax thread has finished reading S_j (p_ready), and P has
+                        // its own columns, so the next block's maxima are computed while P_j V_j runs
+                        ok = mbar_wait(&sh->k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u);
                         if (!ok) break;
-                        if (j + 2 < nkb) load_kv(j + 2);
+                        tc_fence_after();
+                        issue_qk(j + 1);
+                        if (j + 2 < nkb) {
+                            load_k(j + 2);   // K_j's stage: Q K_j^T completed before the softmax of block j began
+                            // V_j's stage is free once P_j V_j has completed
+                            ok = mbar_wait(&sh->pv_done, (uint32_t)j & 1u);
+                            if (!ok) break;
+                            load_v(j + 2);
+                        }
                     }
                 }
                 umma_commit(&sh->o_done);
@@ -249,10 +271,9 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
             const half* mrow = (has_mask && qr < L) ? p.mask + (size_t)qr * p.mask_ld : nullptr;
             const bool mask_vec = has_mask && (p.mask_ld & 7) == 0 && (reinterpret_cast<uintptr_t>(p.mask) & 15) == 0;
             const uint32_t s_addr = tmem + lane_base + (uint32_t)(half_id * 64);           // this thread's S columns
-            const uint32_t p_addr = s_addr;   // its packed P goes over the S columns it has already consumed
+            const uint32_t p_addr = tmem + lane_base + kPCol + (uint32_t)(half_id * 32);   // its 64 keys as packed fp16
             const uint32_t o_addr = tmem + lane_base + kOCol + (uint32_t)(half_id * 32);   // the O columns it rescales/stores
-            const uint32_t sum_addr = tmem + lane_base + kSumCol;
-            float m_run = -INFINITY;
+            float m_run = -INFINITY, l_run = 0.f;   // running maximum of the row, running sum of this half-row
             bool ok = true;
             for (int j = 0; j < nkb; ++j) {
                 int got = 1;
@@ -271,6 +292,20 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                 // pass 1: maximum of the scaled, masked scores of this half-row, then of the whole row
                 float bmax = -INFINITY;
                 const bool all_valid = k0 + 64 <= valid;   // uniform per warp: no per-key validity selects needed
+                if (!has_mask && all_valid) {
+                    // the common case: both 32-column loads in flight at once, one wait
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(s_addr, r0);
+                    tmem_ld32(s_addr + 32, r1);
+                    tmem_ld_wait();
+                    float raw0 = -INFINITY, raw1 = -INFINITY;   // the scale is positive: scale the maximum once
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        raw0 = fmaxf(raw0, __uint_as_float(r0[i]));
+                        raw1 = fmaxf(raw1, __uint_as_float(r1[i]));
+                    }
+                    bmax = fmaxf(raw0, raw1) * p.scale_log2;
+                } else
                 for (int c = 0; c < 2; ++c) {
                     uint32_t r[32];
                     tmem_ld32(s_addr + c * 32, r);
@@ -301,12 +336,30 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                 named_pair_sync(1 + quarter);
                 bmax = fmaxf(bmax, sh->xmax[half_id ^ 1][row]);
                 if (tid == 0) AT_STAMP(31 + 4 * j);
-                const float m_new = fmaxf(m_run, bmax);
+                // The reference point of the exponentials moves only when the row maximum has grown by more than 2^8
+                // since it was set: P stays below 256 (fine in fp16, sums in fp32) and most blocks skip the rescaling
+                // of O. The final division by the row sum makes the result independent of the reference point.
+                const float m_cand = fmaxf(m_run, bmax);
+                const bool grow = m_cand > m_run + kRescaleStep;   // also true for the first block with a finite maximum
+                const float m_new = grow ? m_cand : m_run;
                 const float shift = (m_new == -INFINITY) ? 0.f : m_new;
-                const float alpha = ex2_fast(m_run - shift);    // 0 when there was no previous block
-                // O accumulates in tensor memory; P_{j-1} V_{j-1} has completed (the issuer waited for it before
-                // it started this block's Q K^T). Each thread rescales its 32 of the 64 columns.
+                const float alpha = grow ? ex2_fast(m_run - shift) : 1.f;    // 0 when there was no previous block
+                const bool any_grow = __any_sync(0xffffffffu, grow);
+                // O accumulates in tensor memory. P_{j-1} V_{j-1} must have completed before O is rescaled and before
+                // the P columns are written again. Each thread rescales its 32 of the 64 columns.
                 if (j > 0) {
+                    int pv = 1;
+                    if (lane == 0) pv = (!sh->abort && mbar_wait(&sh->pv_done, (uint32_t)(j - 1) & 1u)) ? 1 : 0;
+                    pv = __shfl_sync(0xffffffffu, pv, 0);
+                    if (!pv) {
+                        ok = false;
+                        sh->abort = 1;
+                        for (int jj = j + 1; jj < nkb; ++jj) named_pair_sync(1 + quarter);
+                        break;
+                    }
+                    tc_fence_after();
+                    l_run *= alpha;
+                    if (any_grow)
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         uint32_t r[16];
@@ -316,18 +369,29 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                         for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
                         tmem_st16(o_addr + c * 16, r);
                     }
-                    if (half_id == 0) {   // the row sums accumulate next to O and are rescaled with it
-                        uint32_t r[16];
-                        tmem_ld16(sum_addr, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st16(sum_addr, r);
-                    }
                 }
                 if (tid == 0) AT_STAMP(32 + 4 * j);
                 // pass 2: P = 2^(s - max) as packed fp16 into the P columns
                 const float nshift = -shift;
+                if (!has_mask && all_valid) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld32(s_addr, r0);
+                    tmem_ld32(s_addr + 32, r1);
+                    tmem_ld_wait();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r0[i]), p.scale_log2, nshift),
+                                                  fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, nshift)));
+                    tmem_st16(p_addr, pk);
+                    l_run += sum_packed(pk);
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r1[i]), p.scale_log2, nshift),
+                                                  fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, nshift)));
+                    tmem_st16(p_addr + 16, pk);
+                    l_run += sum_packed(pk);
+                } else
                 for (int c = 0; c < 2; ++c) {
                     uint32_t r[32];
                     tmem_ld32(s_addr + c * 32, r);
@@ -359,6 +423,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                         }
                     }
                     tmem_st16(p_addr + c * 16, pk);
+                    l_run += sum_packed(pk);
                 }
                 m_run = m_new;
                 tmem_st_wait();
@@ -372,11 +437,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
             fin = __shfl_sync(0xffffffffu, fin, 0);
             tc_fence_after();
             if (tid == 0) AT_STAMP(50);
+            // the row sum is the sum of the two half-rows (both are on the scale of the common running maximum)
+            sh->xmax[half_id][row] = l_run;
+            named_pair_sync(1 + quarter);
             if (fin) {
-                uint32_t sr[16];
-                tmem_ld16(sum_addr, sr);
-                tmem_ld_wait();
-                const float l = __uint_as_float(sr[0]);
+                const float l = l_run + sh->xmax[half_id ^ 1][row];
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 half* zrow = p.Z + (size_t)(tok0 + qr) * p.z_pitch + h * kHD + half_id * 32;
 #pragma unroll
