@@ -4,6 +4,7 @@
 // of at least buffer_size(...) bytes; the linears are consumed (moved from).
 #pragma once
 #include <cstddef>
+#include <vector>
 #include "Linear.h"
 #include "utils.h"
 
@@ -21,6 +22,7 @@ class Encoder_base {
     Encoder_base(const Encoder_base&) = delete;
     Encoder_base& operator=(const Encoder_base&) = delete;
     virtual ~Encoder_base() { et_encoder_destroy(enc_); }
+    et_encoder* handle() { return enc_; }
 
     // One sequence of seq_len tokens; out may alias in. Runs on the default stream without host synchronisation.
     virtual void run(half* out, half* in) {
@@ -109,5 +111,33 @@ class Encoder_length : public Encoder_base {
     }
     static size_t buffer_size(int d_model_, int seq_len_, int nheads_) {
         return et_encoder_buffer_size(2, d_model_, seq_len_, nheads_);
+    }
+};
+
+// Extension (no counterpart in the reference, whose callers run one layer object once, test/tile_test.cu:36-41):
+// a stack of layers run back to back on packed tokens with model-owned scratch, replayed as one CUDA graph.
+// The layers are consumed: after add() the encoder object is an empty shell and must not be run.
+class Encoder_stack {
+    et_model* model_ = nullptr;
+    std::vector<et_encoder*> pending_;
+
+  public:
+    Encoder_stack() = default;
+    Encoder_stack(const Encoder_stack&) = delete;
+    Encoder_stack& operator=(const Encoder_stack&) = delete;
+    ~Encoder_stack() { et_model_destroy(model_); }
+
+    // Layers in order; call before the first run_batch().
+    void add(Encoder_base& layer) { pending_.push_back(layer.handle()); }
+
+    void run_batch(half* out, half* in, const int* seq_lens, int batch, cudaStream_t stream = nullptr,
+                   const int* valid_lens = nullptr) {
+        if (!model_) et_shim::require_ok(et_model_create(&model_, pending_.data(), (int)pending_.size()), "Encoder_stack");
+        et_shim::require_ok(et_model_run_batch(model_, out, in, seq_lens, valid_lens, batch, stream),
+                            "Encoder_stack::run_batch");
+    }
+    void reserve(int total_tokens, int batch, int max_len) {
+        if (!model_) et_shim::require_ok(et_model_create(&model_, pending_.data(), (int)pending_.size()), "Encoder_stack");
+        et_shim::require_ok(et_model_reserve(model_, total_tokens, batch, max_len), "Encoder_stack::reserve");
     }
 };
