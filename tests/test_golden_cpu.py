@@ -17,7 +17,7 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref
 @pytest.fixture(scope="module")
 def gold():
     if not os.path.exists(GOLDEN):
-        pytest.skip("tests/golden/reference_kernels.npz is missing: run tests/golden/make_golden.py on a GPU box")
+        pytest.fail("tests/golden/reference_kernels.npz is missing: run tests/golden/make_golden.py on a GPU box")
     return np.load(GOLDEN)
 
 
