@@ -65,12 +65,6 @@ struct GemmParams {
     half* Y;
     const half* bias;
     int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, stages, a_slots, epi_bufs, gelu;
-    // K split: `ksplit` CTAs share an output tile, each taking a contiguous range of K chunks. They leave fp32
-    // partial sums in `ws` ([ksplit][ws_rows][N]); the one that arrives last at the tile's counter adds them up
-    // and writes the output. Nobody waits for anybody.
-    int ksplit, ws_rows;
-    float* ws;
-    unsigned* counters;
     int* err;
     uint2 first[kDirInParams];   // dir[chunk][0] for chunk < kDirInParams: no global load before the first TMA
     long long* prof;         // optional per-role clock64 stamps of CTA (0,0) (ET_GEMM_PROFILE builds only)
@@ -128,7 +122,6 @@ struct Shared {
     uint64_t acc_done;            // 8 issuer commits after a tile's last chunk
     uint32_t tmem_base;
     volatile int abort;            // any role gave up: everybody winds down
-    volatile int last_split;       // K split: this CTA arrived last at its tile's counter
     volatile int issuer_abort[2];  // [tile parity]: set by an issuer warp that gives up during a tile, read by
                                    // all of them after the named barrier that opens the next tile, so that
                                    // the eight warps leave the tile loop at the same tile
@@ -141,19 +134,6 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 }
 __device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
     asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-// tile index -> (slab, chunk of block-rows, range of K chunks, K split). Splits of one output tile are adjacent.
-struct TileId { int slab, chunk, split, kc0, kc1, out; };
-__device__ __forceinline__ TileId decode_tile(const GemmParams& p, int tile) {
-    TileId t;
-    t.out = tile / p.ksplit;
-    t.split = tile - t.out * p.ksplit;
-    t.slab = t.out / p.n_chunks;
-    t.chunk = t.out - t.slab * p.n_chunks;
-    t.kc0 = t.split * p.k_chunks / p.ksplit;
-    t.kc1 = (t.split + 1) * p.k_chunks / p.ksplit;
-    return t;
 }
 
 // One 32-column unit of the epilogue, in three steps so that two units can be in flight per warp.
@@ -248,16 +228,15 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         uint32_t phb = 0;
         bool alive = true;
         for (int tl = 0; tl < my_tiles && alive; ++tl) {
-            const TileId t = decode_tile(p, (int)blockIdx.x + tl * G);
-            const int slab = t.slab, chunk = t.chunk;
+            const int tile = (int)blockIdx.x + tl * G;
+            const int slab = tile / p.n_chunks, chunk = tile - slab * p.n_chunks;
             const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
             // directory entries: the first one of the first tile comes from the kernel parameters, the others are
             // fetched one chunk ahead
-            uint2 dnext = (tl == 0 && t.kc0 == 0 && chunk < kDirInParams) ? p.first[chunk]
-                          : (lane == 0 ? __ldg(gdir + t.kc0) : make_uint2(0, 0));
-            for (int kc = t.kc0; kc < t.kc1; ++kc) {
+            uint2 dnext = (tl == 0 && chunk < kDirInParams) ? p.first[chunk] : (lane == 0 ? __ldg(gdir) : make_uint2(0, 0));
+            for (int kc = 0; kc < p.k_chunks; ++kc) {
                 const uint2 d = dnext;
-                if (lane == 0 && kc + 1 < t.kc1) dnext = __ldg(gdir + kc + 1);
+                if (lane == 0 && kc + 1 < p.k_chunks) dnext = __ldg(gdir + kc + 1);
                 int go = 1;
                 if (lane == 1)
                     go = (!sh->abort && mbar_wait(&sh->done[bs], phb ^ 1u)) ? 1 : 0;
@@ -308,20 +287,17 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         named_barrier_sync(2, kThreads);        // + the producer's arrive: mbarriers are initialised
         tc_fence_after();
         if (tid == 32) ET_STAMP(2);
+        const int n_items = my_tiles * p.k_chunks;
 
         if (warp < kFirstIssuer) {
             // ---------------- movers: shared memory -> tensor memory copy of the A operand. The mover warps take
-            // chunks in turn (a warp needs ~1500 clocks per chunk: one or two barrier waits, eight tcgen05.cp, a
-            // commit); lane 1 polls, lane 0 issues and commits.
+            // chunks in turn (a warp needs ~1500 clocks per chunk: two barrier waits, eight tcgen05.cp, two
+            // commits); lane 1 polls, lane 0 issues and commits.
             const int m = warp - 1;
-            int bs = 0, a = 0, it = 0;
-            uint32_t phb = 0;
-            bool alive = true;
-            for (int tl = 0; tl < my_tiles && alive; ++tl) {
-              const TileId t = decode_tile(p, (int)blockIdx.x + tl * G);
-              for (int kc = t.kc0; kc < t.kc1; ++kc, ++it) {
-                if ((it % kMovers) == m) {
-                if (sh->abort) { alive = false; break; }
+            int bs = m % DB, a = m % RA;
+            uint32_t phb = (uint32_t)(m / DB) & 1u;
+            for (int it = m; it < n_items; it += kMovers) {
+                if (sh->abort) break;
                 int got = 1;
                 if (lane == 1) {
                     got = mbar_wait(&sh->full[bs], phb);
@@ -337,7 +313,6 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 if (!got) {
                     if (lane == 0) atomicExch(p.err, 12);
                     sh->abort = 1;
-                    alive = false;
                     break;
                 }
                 tc_fence_after();
@@ -354,10 +329,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     if (it < 64) ET_STAMP(300 + it);
                 }
                 __syncwarp();
-                }
-                if (++bs == DB) { bs = 0; phb ^= 1u; }
-                if (++a == RA) a = 0;
-              }
+                bs += kMovers;
+                while (bs >= DB) { bs -= DB; phb ^= 1u; }
+                a = (a + kMovers) % RA;
             }
         } else {
             // ---------------- issuers: one UMMA per kept tile, A from tensor memory; then the tile's epilogue
@@ -372,11 +346,11 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             uint8_t* const buf1 = buf0 + kUnitBytes;
             const int ustep = 2 * p.epi_bufs;
             bool ok = true;
-            int bs = 0, a = 0, nchunk = 0;
+            int bs = 0, a = 0;
             uint32_t pha = 0;
             for (int tl = 0; tl < my_tiles; ++tl) {
-                const TileId t = decode_tile(p, (int)blockIdx.x + tl * G);
-                const int slab = t.slab, chunk = t.chunk;
+                const int tile = (int)blockIdx.x + tl * G;
+                const int slab = tile / p.n_chunks, chunk = tile - slab * p.n_chunks;
                 half* const tbias = sh->bias[tl & 1];
                 {
                     const int col0 = chunk * p.nb * 16;
@@ -388,7 +362,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 named_barrier_sync(3, 32 * kIssuers);
                 if (tl > 0 && sh->issuer_abort[(tl - 1) & 1]) break;
                 tc_fence_after();
-                for (int kc = t.kc0; kc < t.kc1 && ok; ++kc, ++nchunk) {
+                for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
                     if (sh->abort) {
                         sh->issuer_abort[tl & 1] = 1;
                         ok = false;
@@ -398,7 +372,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     int got = 1;
                     if (lane == 1) {
                         got = mbar_wait(&sh->a_ready[a], pha);
-                        if (w == 0 && nchunk < 64) ET_STAMP(500 + nchunk);
+                        if (w == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(500 + tl * p.k_chunks + kc);
                     }
                     got = __shfl_sync(0xffffffffu, got, 1);
                     if (!got) {
@@ -423,7 +397,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                             umma_f16_ts(tmem + e.z, abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
                     }
                     if (elect_one()) umma_commit(&sh->done[bs]);
-                    if (w == 0 && lane == 0 && nchunk < 64) ET_STAMP(600 + nchunk);
+                    if (w == 0 && lane == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(600 + tl * p.k_chunks + kc);
                     __syncwarp();
                     if (++bs == DB) bs = 0;
                     if (++a == RA) { a = 0; pha ^= 1u; }
@@ -450,78 +424,6 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 const int units = (p.nb + 1) >> 1;
                 const bool more = tl + 1 < my_tiles;
                 const int col0 = chunk * p.nb * 16, row0 = slab * kSlab + q * 32;
-                if (p.ksplit > 1) {
-                    // ---- K split: partial sums to the workspace; the CTA that arrives last adds them up
-                    const int row = row0 + lane;
-                    float* const wrow = p.ws + ((size_t)t.split * p.ws_rows + row) * p.N + col0;
-                    for (int u = h; u < units && ok; u += 2) {
-                        const bool two = u * 2 + 1 < p.nb;
-                        uint32_t acc[32];
-                        epi_load(tmem + lane_base + u * 32, two, acc);
-                        tmem_ld_wait();
-                        if (more) {
-                            tmem_st16_zero(tmem + lane_base + u * 32);
-                            if (two) tmem_st16_zero(tmem + lane_base + u * 32 + 16);
-                        }
-                        if (row < p.T) {
-                            uint4* dst = reinterpret_cast<uint4*>(wrow + u * kUnitCols);
-                            const int nq = (col0 + u * kUnitCols + 16 < p.N && two) ? 8 : (col0 + u * kUnitCols < p.N ? 4 : 0);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                if (i < nq) dst[i] = make_uint4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
-                        }
-                    }
-                    __threadfence();
-                    named_barrier_sync(3, 32 * kIssuers);
-                    if (w == 0 && lane == 0) {
-                        const unsigned old = atomicAdd(p.counters + t.out, 1u);
-                        const int last = (!sh->abort && old == (unsigned)p.ksplit - 1u) ? 1 : 0;
-                        if (last) p.counters[t.out] = 0u;   // everybody has arrived: ready for the next launch
-                        sh->last_split = last;
-                    }
-                    named_barrier_sync(3, 32 * kIssuers);
-                    if (sh->last_split) {
-                        __threadfence();
-                        for (int u = h; u < units && ok; u += 2) {
-                            const bool two = u * 2 + 1 < p.nb;
-                            const int nq = (col0 + u * kUnitCols + 16 < p.N && two) ? 8 : (col0 + u * kUnitCols < p.N ? 4 : 0);
-                            float4 sum[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (row < p.T) {
-                                for (int sp = 0; sp < p.ksplit; ++sp) {
-                                    const float4* src = reinterpret_cast<const float4*>(
-                                        p.ws + ((size_t)sp * p.ws_rows + row) * p.N + col0 + u * kUnitCols);
-#pragma unroll
-                                    for (int i = 0; i < 8; ++i)
-                                        if (i < nq) {
-                                            const float4 v = __ldcg(src + i);
-                                            sum[i].x += v.x; sum[i].y += v.y; sum[i].z += v.z; sum[i].w += v.w;
-                                        }
-                                }
-                            }
-                            uint32_t acc[32];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                acc[4 * i] = __float_as_uint(sum[i].x);
-                                acc[4 * i + 1] = __float_as_uint(sum[i].y);
-                                acc[4 * i + 2] = __float_as_uint(sum[i].z);
-                                acc[4 * i + 3] = __float_as_uint(sum[i].w);
-                            }
-                            uint4 ov[4];
-                            epi_convert<kGelu>(acc, tbias + u * 32, two, ov);
-                            if (lane == 0) tma_store_wait_read();
-                            __syncwarp();
-                            epi_write(buf0, lane, ov);
-                            fence_proxy_async_smem();
-                            __syncwarp();
-                            if (lane == 0) {
-                                if (col0 + u * kUnitCols < p.N) tma_store_2d(&tmY, buf0, col0 + u * kUnitCols, row0);
-                                tma_store_commit();
-                            }
-                        }
-                    }
-                } else
                 for (int u = h; u < units && ok; u += ustep) {
                     const int u2 = u + 2;
                     const bool second = p.epi_bufs == 2 && u2 < units;
@@ -577,9 +479,6 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 
 struct TileWeight {
     int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, stages = 0, a_slots = 0, epi_bufs = 1;
-    int ksplit = 1, ws_rows = 0;
-    float* d_ws = nullptr;
-    unsigned* d_counters = nullptr;
     long ntile = 0;
     int size_hint = 0;
     // the caller's arrays, kept so that weights can be concatenated (Q|K|V in one launch) and re-packed
@@ -615,14 +514,11 @@ static RingShape ring_shape(int nb, int stage_b_bytes) {
 // Block-rows per CTA from a model of the persistent kernel: a chunk takes the ring period, or its UMMAs (~10
 // clocks each with eight issuing warps), or its share of L2 bandwidth (~64 bytes per clock per SM), whichever
 // is longest; a tile ends with an epilogue of ~350 clocks per 32 columns and warp.
-// K split (1 = none): when the tiles do not fill the SMs and K is long, `ksplit` CTAs share an output tile.
-constexpr size_t kMaxSplitWorkspace = (size_t)64 << 20;
-static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double density, int out_feat, int* ksplit) {
+static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double density) {
     const int slabs = std::max(1, (size_hint + kSlab - 1) / kSlab);
     const int sms = std::max(1, sm_count());
     double best = 0;
     int best_nb = 0;
-    *ksplit = 1;
     for (int nb : {24, 20, 16, 12, 8, 4}) {
         // chunks other than a single one must cover whole 64-column output panels (nb % 4 == 0)
         const int nbe = n_block_rows <= nb ? std::max(n_block_rows, 1) : nb;
@@ -634,21 +530,13 @@ static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double densi
         const int stage_b = (int)((kHeaderBytes + tiles_max * 528.0 + 1023) / 1024) * 1024;
         const RingShape rs = ring_shape(nbe, stage_b);
         if (rs.stages < 2 || rs.a_slots < 1) continue;
-        const long out_tiles = (long)slabs * ((n_block_rows + nbe - 1) / nbe);
+        const long tiles = (long)slabs * ((n_block_rows + nbe - 1) / nbe);
+        const double per_cta = (double)((tiles + sms - 1) / sms);
         const double t_chunk = std::max({rs.period, 10.0 * tiles_per_chunk,
                                          (kXStageBytes + tiles_per_chunk * 528.0) / 64.0});
-        for (int ks : {1, 2, 3, 4, 6, 8, 12}) {
-            if (ks > 1 && (k_chunks / ks < 2 || out_tiles * ks > sms ||
-                           (size_t)ks * slabs * kSlab * out_feat * sizeof(float) > kMaxSplitWorkspace))
-                continue;
-            const long tiles = out_tiles * ks;
-            const double per_cta = (double)((tiles + sms - 1) / sms);
-            const double epi = 350.0 * ((nbe + 3) / 4);
-            // a split CTA writes its partial sums; the last one also reads all of them and stores the output
-            const double t_tile = ((k_chunks + ks - 1) / ks) * t_chunk + (ks > 1 ? 2.0 * epi + 150.0 * ks * ((nbe + 3) / 4) + 800.0 : epi) + 800.0;
-            const double cost = per_cta * t_tile + 3000.0;
-            if (best_nb == 0 || cost < best * 0.999) { best = cost; best_nb = nbe; *ksplit = ks; }
-        }
+        const double t_tile = k_chunks * t_chunk + 350.0 * ((nbe + 3) / 4) + 800.0;
+        const double cost = per_cta * t_tile + 3000.0;
+        if (best_nb == 0 || cost < best * 0.999) { best = cost; best_nb = nbe; }
     }
     return best_nb > 0 ? best_nb : std::min(8, std::max(n_block_rows, 1));
 }
@@ -669,14 +557,12 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     auto* w = new TileWeight();
     w->K = K; w->N = N; w->ntile = ntile; w->size_hint = size_hint;
     const double density = (double)ntile / std::max(1.0, (double)NBR * (K / 16));
-    w->nb = choose_nb(NBR, (K + kKC - 1) / kKC, size_hint, density, N, &w->ksplit);
+    w->nb = choose_nb(NBR, (K + kKC - 1) / kKC, size_hint, density);
     if (nb_override <= 0 && g_tune[0] > 0) nb_override = g_tune[0];
     if (nb_override > 0) {
         const int nbo = std::min(nb_override, kMaxNB);
         w->nb = NBR <= nbo ? NBR : std::max(4, nbo / 4 * 4);
-        w->ksplit = 1;
     }
-    if (g_tune[2] > 0) w->ksplit = std::min(g_tune[2], std::max(1, (K + kKC - 1) / kKC));   // tuning experiments
     w->h_row_ptr.assign(row_ptr, row_ptr + NBR + 1);
     w->h_row_offset.assign(row_offset, row_offset + ntile);
     w->h_data.assign(data, data + (size_t)ntile * 256);
@@ -745,18 +631,6 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     cudaError_t e3 = cudaMalloc(&w->d_bias, (size_t)N * sizeof(half));
     cudaError_t e4 = cudaMalloc(&w->d_err, sizeof(int));
     if (e1 || e2 || e3 || e4) { tile_weight_free(w); return fail(ET_ERR_CUDA, "tile weight: cudaMalloc failed"); }
-    if (w->ksplit > 1) {
-        // K split: fp32 partial sums [ksplit][rows][N] and one arrival counter per output tile; both are sized
-        // for the token count announced at construction
-        w->ws_rows = std::max(1, (size_hint + kSlab - 1) / kSlab) * kSlab;
-        const size_t ncount = (size_t)(w->ws_rows / kSlab) * w->n_chunks;
-        if (cudaMalloc(&w->d_ws, (size_t)w->ksplit * w->ws_rows * N * sizeof(float)) != cudaSuccess ||
-            cudaMalloc(&w->d_counters, ncount * sizeof(unsigned)) != cudaSuccess) {
-            tile_weight_free(w);
-            return fail(ET_ERR_CUDA, "tile weight: cudaMalloc failed");
-        }
-        cudaMemset(w->d_counters, 0, ncount * sizeof(unsigned));
-    }
     cudaMemcpy(w->d_dir, dir.data(), dir.size() * sizeof(uint2), cudaMemcpyHostToDevice);
     cudaMemcpy(w->d_stream, stream.data(), stream.size(), cudaMemcpyHostToDevice);
     if (bias) cudaMemcpy(w->d_bias, bias, (size_t)N * sizeof(half), cudaMemcpyHostToDevice);
@@ -791,7 +665,6 @@ int tile_weight_concat(TileWeight** out, const TileWeight* const* parts, int cou
 void tile_weight_free(TileWeight* w) {
     if (!w) return;
     cudaFree(w->d_dir); cudaFree(w->d_stream); cudaFree(w->d_bias); cudaFree(w->d_err);
-    cudaFree(w->d_ws); cudaFree(w->d_counters);
     delete w;
 }
 
@@ -826,10 +699,7 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     p.dir = w->d_dir; p.stream = w->d_stream; p.Y = Y; p.bias = w->d_bias;
     p.T = T; p.N = w->N; p.k_chunks = w->k_chunks; p.nb = w->nb;
     p.n_chunks = w->n_chunks;
-    // the K split needs the workspace sized at construction: more tokens than that run unsplit
-    p.ksplit = (w->ksplit > 1 && T <= w->ws_rows) ? w->ksplit : 1;
-    p.ws = w->d_ws; p.ws_rows = w->ws_rows; p.counters = w->d_counters;
-    p.n_tiles = ((T + kSlab - 1) / kSlab) * w->n_chunks * p.ksplit;
+    p.n_tiles = ((T + kSlab - 1) / kSlab) * w->n_chunks;
     p.stage_b_bytes = w->stage_b_bytes; p.stages = w->stages; p.a_slots = w->a_slots; p.epi_bufs = w->epi_bufs; p.gelu = gelu; p.err = w->d_err;
     p.prof = g_prof;
     for (size_t c = 0; c < w->h_first.size(); ++c) p.first[c] = w->h_first[c];
@@ -849,18 +719,13 @@ int tile_weight_error(const TileWeight* w, int* code) {
     cudaError_t e = cudaMemcpy(&v, w->d_err, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_status(e, "tile weight error read");
     *code = v;
-    if (v) {
-        cudaMemset(w->d_err, 0, sizeof(int));
-        // a CTA that gave up may not have arrived at its tile's counter
-        if (w->d_counters) cudaMemset(w->d_counters, 0, (size_t)(w->ws_rows / kSlab) * w->n_chunks * sizeof(unsigned));
-    }
+    if (v) cudaMemset(w->d_err, 0, sizeof(int));
     return ET_OK;
 }
 
 void tile_weight_info(const TileWeight* w, int* info) {
     info[0] = w->nb; info[1] = w->n_chunks; info[2] = w->k_chunks; info[3] = w->stages;
     info[4] = w->stage_b_bytes; info[5] = (int)std::min<size_t>(w->stream_bytes, 0x7fffffff);
-    info[6] = w->ksplit; info[7] = 0;
 }
 
 // ---- launcher-level entry with device-resident BSR arrays: packed form cached per weight ----

@@ -19,7 +19,7 @@ int tile_weight_set_bias_device(TileWeight* w, const half* bias_dev, cudaStream_
 int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st);
 // Reads and clears the device error word (0 = no bounded wait gave up). Synchronises.
 int tile_weight_error(const TileWeight* w, int* code);
-void tile_weight_info(const TileWeight* w, int* info8);
+void tile_weight_info(const TileWeight* w, int* info6);
 int tile_spmm_raw(half* Y, const half* X, const int* row_ptr, const int* row_offset, const half* data,
                   int M, int N, int K, const half* bias, int gelu, cudaStream_t st);
 void tile_spmm_cache_clear();

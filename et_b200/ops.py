@@ -64,9 +64,9 @@ class TileWeight:
         check(lib().et_tile_weight_check(self._h, ctypes.byref(code)))
 
     def info(self):
-        arr = (ctypes.c_int * 8)()
+        arr = (ctypes.c_int * 6)()
         check(lib().et_tile_weight_info(self._h, arr))
-        return dict(zip(["nb", "n_chunks", "k_chunks", "stages", "stage_bytes", "packed_bytes", "k_split"], arr))
+        return dict(zip(["nb", "n_chunks", "k_chunks", "stages", "stage_bytes", "packed_bytes"], arr))
 
     def close(self):
         if self._h:

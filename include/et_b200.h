@@ -59,7 +59,7 @@ int et_tile_linear(const et_tile_weight* w, void* Y, const void* X, int tokens, 
 /* Reads and clears the weight's device error word (synchronises): ET_ERR_DEVICE_TIMEOUT and the
  * code in *code when a bounded wait inside the kernel gave up since the last check. */
 int et_tile_weight_check(const et_tile_weight* w, int* code);
-/* info[8] = {block_rows_per_cta, n_chunks, k_chunks, stages, stage_bytes, packed_bytes, k_split, 0}. */
+/* info[6] = {block_rows_per_cta, n_chunks, k_chunks, stages, stage_bytes, packed_bytes}. */
 int et_tile_weight_info(const et_tile_weight* w, int* info);
 /* Same contraction from DEVICE-resident tile arrays, K = in_feat explicit. The packed form of a
  * weight is built on its first use (device-to-host copy, synchronous) and cached by array address;

@@ -143,57 +143,6 @@ def test_tile_linear_all_chunkings(et, orc, size_hint):
     util.assert_close(got, want, what=f"tile linear hint {size_hint} {w.info()}")
 
 
-@pytest.mark.parametrize("T,K,N,sparsity,gelu", [
-    (128, 3072, 768, 0.75, False),    # one slab, long K: the pack splits K over several CTAs per output tile
-    (128, 768, 768, 0.0, True),       # dense single sequence
-    (200, 1536, 320, 0.5, True),      # ragged rows, N not a multiple of 32 x chunks
-    (2048, 3072, 768, 0.75, False),   # FFN2 of the bench workload
-])
-def test_tile_linear_k_split(et, orc, T, K, N, sparsity, gelu):
-    """K split: several CTAs share an output tile, partial sums meet in a workspace, the last arrival writes.
-    Repeated launches reuse the arrival counters; more tokens than announced at construction run unsplit."""
-    rp, ro, data, bias = util.make_tile_linear(orc, K, N, sparsity, T + K, True, 0.05)
-    w = et.TileWeight(K, N, T, data, rp, ro, bias, is_gelu=gelu)
-    for rep in range(3):
-        X = util.activations(T + rep, (T, K))
-        Y = torch.full((T, N), float("nan"), dtype=torch.float16, device="cuda")
-        w.run(Y, dev(X))
-        torch.cuda.synchronize()
-        w.check()
-        util.assert_close(host(Y), orc.tile_linear(X, rp, ro, data, bias, N, gelu=gelu),
-                          what=f"K split T={T} K={K} N={N} launch {rep} {w.info()}")
-    T2 = T + 200
-    X = util.activations(5, (T2, K))
-    Y = torch.full((T2, N), float("nan"), dtype=torch.float16, device="cuda")
-    w.run(Y, dev(X))
-    torch.cuda.synchronize()
-    w.check()
-    util.assert_close(host(Y), orc.tile_linear(X, rp, ro, data, bias, N, gelu=gelu), what="beyond the announced size")
-
-
-def test_tile_linear_forced_k_split_all_factors(et, orc):
-    """Every split factor through the tuning hook (the automatic choice only picks some of them)."""
-    import ctypes
-    T, K, N = 300, 1536, 256
-    rp, ro, data, bias = util.make_tile_linear(orc, K, N, 0.6, 91, True, 0.05)
-    X = util.activations(92, (T, K))
-    want = orc.tile_linear(X, rp, ro, data, bias, N)
-    lib = et.lib()
-    try:
-        for ks in (2, 3, 4, 6, 12):
-            lib.et_debug_set_gemm_tuning(8, 0, ks, 0)
-            w = et.TileWeight(K, N, T, data, rp, ro, bias)
-            assert w.info()["k_split"] == ks
-            for rep in range(2):
-                Y = torch.full((T, N), float("nan"), dtype=torch.float16, device="cuda")
-                w.run(Y, dev(X))
-                torch.cuda.synchronize()
-                w.check()
-                util.assert_close(host(Y), want, what=f"forced K split {ks} launch {rep}")
-    finally:
-        lib.et_debug_set_gemm_tuning(0, 0, 0, 0)
-
-
 def test_tile_linear_pruned_tiles_do_not_contribute(et, orc):
     """Mask exactness: output equals the dense product with the pruned tiles zeroed, and does not
     change when garbage is placed where the pruned tiles would be."""
