@@ -8,7 +8,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libet_b200.so")
+# ET_B200_LIB points the binding at another build of the library (e.g. a profiling build)
+LIB_PATH = os.environ.get("ET_B200_LIB") or os.path.join(_HERE, "libet_b200.so")
 INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
 
 _lib = None
