@@ -289,77 +289,117 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                 if (tid == 0) AT_STAMP(30 + 4 * j);
                 tc_fence_after();
                 const int k0 = j * kBK + half_id * 64;
-                // pass 1: maximum of the scaled, masked scores of this half-row, then of the whole row
-                float bmax = -INFINITY;
                 const bool all_valid = k0 + 64 <= valid;   // uniform per warp: no per-key validity selects needed
-                if (!has_mask && all_valid) {
-                    // the common case: both 32-column loads in flight at once, one wait
-                    uint32_t r0[32], r1[32];
-                    tmem_ld32(s_addr, r0);
-                    tmem_ld32(s_addr + 32, r1);
-                    tmem_ld_wait();
-                    float raw0 = -INFINITY, raw1 = -INFINITY;   // the scale is positive: scale the maximum once
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        raw0 = fmaxf(raw0, __uint_as_float(r0[i]));
-                        raw1 = fmaxf(raw1, __uint_as_float(r1[i]));
-                    }
-                    bmax = fmaxf(raw0, raw1) * p.scale_log2;
-                } else
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(s_addr + c * 32, r);
-                    tmem_ld_wait();
-                    const int kc = k0 + c * 32;
-                    if (has_mask) {
-                        float mk[32];
-                        load_mask32(mk, mrow, kc, valid, mask_vec);
+                const bool plain = !has_mask && all_valid;
+
+                // Maximum of the scaled, masked scores of this half-row (log2 domain).
+                auto half_row_max = [&]() -> float {
+                    float bmax = -INFINITY;
+                    if (plain) {
+                        // the common case: both 32-column loads in flight at once, one wait
+                        uint32_t r0[32], r1[32];
+                        tmem_ld32(s_addr, r0);
+                        tmem_ld32(s_addr + 32, r1);
+                        tmem_ld_wait();
+                        float raw0 = -INFINITY, raw1 = -INFINITY;   // the scale is positive: scale the maximum once
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            const float v = fmaf(__uint_as_float(r[i]), p.scale_log2, mk[i]);
-                            bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
+                            raw0 = fmaxf(raw0, __uint_as_float(r0[i]));
+                            raw1 = fmaxf(raw1, __uint_as_float(r1[i]));
                         }
-                    } else if (all_valid) {
-                        float raw = -INFINITY;   // the scale is positive: scale the maximum once
+                        return fmaxf(raw0, raw1) * p.scale_log2;
+                    }
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(s_addr + c * 32, r);
+                        tmem_ld_wait();
+                        const int kc = k0 + c * 32;
+                        if (has_mask) {
+                            float mk[32];
+                            load_mask32(mk, mrow, kc, valid, mask_vec);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) raw = fmaxf(raw, __uint_as_float(r[i]));
-                        bmax = fmaxf(bmax, raw * p.scale_log2);
-                    } else {
+                            for (int i = 0; i < 32; ++i) {
+                                const float v = fmaf(__uint_as_float(r[i]), p.scale_log2, mk[i]);
+                                bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
+                            }
+                        } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const float v = __uint_as_float(r[i]) * p.scale_log2;
-                            bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
+                            for (int i = 0; i < 32; ++i) {
+                                const float v = __uint_as_float(r[i]) * p.scale_log2;
+                                bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
+                            }
                         }
                     }
-                }
-                sh->xmax[half_id][row] = bmax;
-                named_pair_sync(1 + quarter);
-                bmax = fmaxf(bmax, sh->xmax[half_id ^ 1][row]);
-                if (tid == 0) AT_STAMP(31 + 4 * j);
-                // The reference point of the exponentials moves only when the row maximum has grown by more than 2^8
-                // since it was set: P stays below 256 (fine in fp16, sums in fp32) and most blocks skip the rescaling
-                // of O. The final division by the row sum makes the result independent of the reference point.
-                const float m_cand = fmaxf(m_run, bmax);
-                const bool grow = m_cand > m_run + kRescaleStep;   // also true for the first block with a finite maximum
-                const float m_new = grow ? m_cand : m_run;
-                const float shift = (m_new == -INFINITY) ? 0.f : m_new;
-                const float alpha = grow ? ex2_fast(m_run - shift) : 1.f;    // 0 when there was no previous block
-                const bool any_grow = __any_sync(0xffffffffu, grow);
-                // O accumulates in tensor memory. P_{j-1} V_{j-1} must have completed before O is rescaled and before
-                // the P columns are written again. Each thread rescales its 32 of the 64 columns.
-                if (j > 0) {
-                    int pv = 1;
-                    if (lane == 0) pv = (!sh->abort && mbar_wait(&sh->pv_done, (uint32_t)(j - 1) & 1u)) ? 1 : 0;
-                    pv = __shfl_sync(0xffffffffu, pv, 0);
-                    if (!pv) {
-                        ok = false;
-                        sh->abort = 1;
-                        for (int jj = j + 1; jj < nkb; ++jj) named_pair_sync(1 + quarter);
-                        break;
+                    return bmax;
+                };
+                // P = 2^(s - shift) as packed fp16 into the P columns; returns the sum of the fp16 values written and,
+                // through `bmax`, the maximum of the scaled, masked scores seen on the way.
+                auto write_p = [&](float shift, float& bmax) -> float {
+                    const float nshift = -shift;
+                    float lsum = 0.f;
+                    bmax = -INFINITY;
+                    if (plain) {
+                        uint32_t r0[32], r1[32];
+                        tmem_ld32(s_addr, r0);
+                        tmem_ld32(s_addr + 32, r1);
+                        tmem_ld_wait();
+                        uint32_t pk[16];
+                        float raw = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            raw = fmaxf(raw, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1])));
+                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r0[i]), p.scale_log2, nshift),
+                                                      fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, nshift)));
+                        }
+                        tmem_st16(p_addr, pk);
+                        lsum += sum_packed(pk);
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            raw = fmaxf(raw, fmaxf(__uint_as_float(r1[i]), __uint_as_float(r1[i + 1])));
+                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r1[i]), p.scale_log2, nshift),
+                                                      fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, nshift)));
+                        }
+                        tmem_st16(p_addr + 16, pk);
+                        lsum += sum_packed(pk);
+                        bmax = raw * p.scale_log2;
+                        return lsum;
                     }
-                    tc_fence_after();
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t r[32];
+                        tmem_ld32(s_addr + c * 32, r);
+                        tmem_ld_wait();
+                        const int kc = k0 + c * 32;
+                        uint32_t pk[16];
+                        if (has_mask) {
+                            float mk[32];
+                            load_mask32(mk, mrow, kc, valid, mask_vec);
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                float va = fmaf(__uint_as_float(r[i]), p.scale_log2, mk[i]);
+                                float vb = fmaf(__uint_as_float(r[i + 1]), p.scale_log2, mk[i + 1]);
+                                va = (kc + i < valid) ? va : -INFINITY;
+                                vb = (kc + i + 1 < valid) ? vb : -INFINITY;
+                                bmax = fmaxf(bmax, fmaxf(va, vb));
+                                pk[i >> 1] = ex2_h2(pack2(va + nshift, vb + nshift));
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 2) {
+                                const float va = (kc + i < valid) ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
+                                const float vb = (kc + i + 1 < valid) ? __uint_as_float(r[i + 1]) * p.scale_log2 : -INFINITY;
+                                bmax = fmaxf(bmax, fmaxf(va, vb));
+                                pk[i >> 1] = ex2_h2(pack2(va + nshift, vb + nshift));
+                            }
+                        }
+                        tmem_st16(p_addr + c * 16, pk);
+                        lsum += sum_packed(pk);
+                    }
+                    return lsum;
+                };
+                // O and the running sum move to a new reference point (O accumulates in tensor memory; each thread
+                // rescales its 32 of the 64 columns). Only called when P_{j-1} V_{j-1} has completed.
+                auto rescale = [&](float alpha) {
                     l_run *= alpha;
-                    if (any_grow)
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         uint32_t r[16];
@@ -369,63 +409,55 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                         for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
                         tmem_st16(o_addr + c * 16, r);
                     }
-                }
-                if (tid == 0) AT_STAMP(32 + 4 * j);
-                // pass 2: P = 2^(s - max) as packed fp16 into the P columns
-                const float nshift = -shift;
-                if (!has_mask && all_valid) {
-                    uint32_t r0[32], r1[32];
-                    tmem_ld32(s_addr, r0);
-                    tmem_ld32(s_addr + 32, r1);
-                    tmem_ld_wait();
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2)
-                        pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r0[i]), p.scale_log2, nshift),
-                                                  fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, nshift)));
-                    tmem_st16(p_addr, pk);
-                    l_run += sum_packed(pk);
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2)
-                        pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r1[i]), p.scale_log2, nshift),
-                                                  fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, nshift)));
-                    tmem_st16(p_addr + 16, pk);
-                    l_run += sum_packed(pk);
-                } else
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(s_addr + c * 32, r);
-                    tmem_ld_wait();
-                    const int kc = k0 + c * 32;
-                    uint32_t pk[16];
-                    if (has_mask) {
-                        float mk[32];
-                        load_mask32(mk, mrow, kc, valid, mask_vec);
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            float a = fmaf(__uint_as_float(r[i]), p.scale_log2, nshift) + mk[i];
-                            float bq = fmaf(__uint_as_float(r[i + 1]), p.scale_log2, nshift) + mk[i + 1];
-                            a = (kc + i < valid) ? a : -INFINITY;
-                            bq = (kc + i + 1 < valid) ? bq : -INFINITY;
-                            pk[i >> 1] = ex2_h2(pack2(a, bq));
-                        }
-                    } else if (all_valid) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r[i]), p.scale_log2, nshift),
-                                                      fmaf(__uint_as_float(r[i + 1]), p.scale_log2, nshift)));
-                    } else {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const float a = (kc + i < valid) ? fmaf(__uint_as_float(r[i]), p.scale_log2, nshift) : -INFINITY;
-                            const float bq = (kc + i + 1 < valid) ? fmaf(__uint_as_float(r[i + 1]), p.scale_log2, nshift) : -INFINITY;
-                            pk[i >> 1] = ex2_h2(pack2(a, bq));
-                        }
+                };
+
+                if (j == 0) {
+                    // first block: row maximum first, it becomes the reference point of the exponentials
+                    float bmax = half_row_max();
+                    sh->xmax[half_id][row] = bmax;
+                    named_pair_sync(1 + quarter);
+                    bmax = fmaxf(bmax, sh->xmax[half_id ^ 1][row]);
+                    if (tid == 0) AT_STAMP(31 + 4 * j);
+                    m_run = bmax;
+                    float unused;
+                    l_run = write_p((m_run == -INFINITY) ? 0.f : m_run, unused);
+                    if (tid == 0) AT_STAMP(32 + 4 * j);
+                } else {
+                    // later blocks: one pass. P is written against the current reference point while the block
+                    // maximum is taken on the way; only if a row's maximum has grown by more than 2^8 (P could leave
+                    // the fp16 range) the reference moves, O is rescaled and the block is done again. The final
+                    // division by the row sum makes the result independent of the reference point.
+                    // P_{j-1} V_{j-1} must have completed before the P columns are written again; it was issued
+                    // before this block's Q K^T, whose completion has just been seen, so this wait does not block.
+                    int pv = 1;
+                    if (lane == 0) pv = (!sh->abort && mbar_wait(&sh->pv_done, (uint32_t)(j - 1) & 1u)) ? 1 : 0;
+                    pv = __shfl_sync(0xffffffffu, pv, 0);
+                    if (!pv) {
+                        ok = false;
+                        sh->abort = 1;
+                        for (int jj = j; jj < nkb; ++jj) named_pair_sync(1 + quarter);
+                        break;
                     }
-                    tmem_st16(p_addr + c * 16, pk);
-                    l_run += sum_packed(pk);
+                    tc_fence_after();
+                    float bmax;
+                    float lblk = write_p((m_run == -INFINITY) ? 0.f : m_run, bmax);
+                    if (tid == 0) AT_STAMP(31 + 4 * j);
+                    sh->xmax[half_id][row] = bmax;
+                    named_pair_sync(1 + quarter);
+                    bmax = fmaxf(bmax, sh->xmax[half_id ^ 1][row]);
+                    const bool grow = bmax > m_run + kRescaleStep;   // also true when the row had no finite score so far
+                    if (__any_sync(0xffffffffu, grow)) {
+                        const float m_new = grow ? bmax : m_run;
+                        const float shift = (m_new == -INFINITY) ? 0.f : m_new;
+                        tmem_st_wait();   // the first version of P is out of the way
+                        rescale(grow ? ex2_fast(m_run - shift) : 1.f);   // 0 when the row had nothing before
+                        m_run = m_new;
+                        float unused;
+                        lblk = write_p(shift, unused);
+                    }
+                    l_run += lblk;
+                    if (tid == 0) AT_STAMP(32 + 4 * j);
                 }
-                m_run = m_new;
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(&sh->p_ready);
