@@ -5,8 +5,11 @@ Workload (N=1): the tile-pruned BERT-base encoder layer of the `encoder_tile_tes
 (batch 16, seq 128, hidden 768, 12 heads, FFN 3072, fp16 storage, fp32 accumulate, seeded Bernoulli 16x16
 tile mask). A step is one forward of the layer over the whole batch. `value` times the layer with inputs
 resident in HBM; `e2e` times the public call with pinned host buffers (H2D of every step's batch and D2H of its
-result inside the timed region, as a three-stage pipeline on three streams; the figure with a host
-synchronisation after every step is reported beside it). With N ranks each rank runs its own batch (weak scaling, no collective inside the
+result inside the timed region, as a three-stage pipeline on separate streams; the figure with a host
+synchronisation after every step is reported beside it). `--streams` independent batches (default 4) are in
+flight per GPU, one CUDA stream each: the layer's launches are short and rarely fill the GPU, so concurrent
+batches use the SMs a single batch leaves idle; `us_per_layer` is the latency with one batch at a time. The
+reference arm runs with the same number of streams. With N ranks each rank runs its own batch (weak scaling, no collective inside the
 layer) and the output shards are gathered with one NCCL all-gather per step.
 
 Cold-cache rule: the step visits INSTANCES independent copies of the workload (own weights, activations,
@@ -144,19 +147,24 @@ def workload_config(args):
                         f"hidden {D_MODEL}, {NHEAD} heads, FFN {D_FF}, Bernoulli 16x16 tile sparsity {args.sparsity} per GPU",
             "global_batch": BATCH * args.gpus, "seq_len": SEQ, "sparsity": args.sparsity,
             "parallelism": f"dp{args.gpus}" if args.gpus > 1 else "single",
+            "batches_in_flight": f"{args.streams} independent batches per GPU on {args.streams} CUDA streams (step i on stream i mod "
+                                 f"{args.streams}); us_per_layer is the latency with one batch at a time",
             "gather": (f"NCCL all-gather of the output shards, the outputs of {args.gather_every} consecutive steps per collective, "
                        "asynchronous, joined inside the timed region") if args.gpus > 1 else "none",
             "l2": f"inputs larger than L2: {INSTANCES} independent instances of the layer (weights, activations, scratch, about "
                   f"{7 * T * D_MODEL * 2 / 1e6:.0f} MB each) visited round-robin"}
 
 
-def timed(step, steps, finish=None):
+def timed(step, steps, finish=None, start=None):
     """`steps` calls of step(i) between two CUDA events on the current stream; returns ms per step.
-    `finish` (optional) runs before the closing event, e.g. to join collectives still in flight."""
+    `start` (optional) runs right after the opening event (side streams wait for it there), `finish` (optional)
+    runs before the closing event, e.g. to join side streams and collectives still in flight."""
     import torch
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    if start:
+        start()
     for i in range(steps):
         step(i)
     if finish:
@@ -166,13 +174,14 @@ def timed(step, steps, finish=None):
     return e0.elapsed_time(e1) / steps
 
 
-def pipelined_e2e(torch, n_steps, n_inst, h2d, compute, d2h, depth=4):
+def pipelined_e2e(torch, n_steps, n_inst, h2d, compute, d2h, depth=4, comp_streams=None):
     """Seconds per step of a three-stage pipeline over `n_inst` independent buffer sets: the host-to-device copy of
     step i+1 and the device-to-host copy of step i-1 run on their own streams under the layer of step i. Every
     step's input is copied from pinned host memory and its result is copied back inside the timed region; the host
     waits for the result of step i-depth before it enqueues step i (a server consuming results, and a bound on
     the work in flight)."""
-    s_in, s_out, s_comp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    comps = comp_streams or [torch.cuda.current_stream()]   # set k always computes on stream k mod len(comps)
     ev_in = [torch.cuda.Event() for _ in range(n_inst)]
     ev_comp = [torch.cuda.Event() for _ in range(n_inst)]
     ev_out = [torch.cuda.Event() for _ in range(n_inst)]
@@ -187,10 +196,12 @@ def pipelined_e2e(torch, n_steps, n_inst, h2d, compute, d2h, depth=4):
                 s_in.wait_event(ev_comp[k])    # the previous layer on this set has read its input
             h2d(k)
             ev_in[k].record(s_in)
+        s_comp = comps[k % len(comps)]
         s_comp.wait_event(ev_in[k])
         if used[k]:
             s_comp.wait_event(ev_out[k])       # the previous result has left the output buffer
-        compute(k)
+        with torch.cuda.stream(s_comp):
+            compute(k)
         ev_comp[k].record(s_comp)
         with torch.cuda.stream(s_out):
             s_out.wait_event(ev_comp[k])
@@ -255,18 +266,36 @@ def run_reference(args, rank):
 
     insts = [RefInstance(i) for i in range(INSTANCES)]
     scale = ctypes.c_float(1.4426950408889634 / (D_MODEL // NHEAD) ** 0.5)   # base-2 kernel: true softmax
-    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     vp = ctypes.c_void_p
+    # the same number of independent batches in flight as the native arm, one stream each
+    NS = max(d for d in range(1, max(1, args.streams) + 1) if INSTANCES % d == 0)
+    main_stream = torch.cuda.current_stream()
+    streams = [main_stream] + [torch.cuda.Stream() for _ in range(NS - 1)]
 
-    def step(i):
+    def run_on(i, stream):
         it = insts[i % INSTANCES]
         rc = ref.ref_encoder_tile_layer(vp(it.out.data_ptr()), vp(it.x.data_ptr()), vp(it.buf.data_ptr()), it.arr,
                                         *[vp(t.data_ptr()) for t in it.lnd], vp(it.mask.data_ptr()), BATCH, SEQ,
-                                        D_MODEL, NHEAD, D_FF, scale, st)
+                                        D_MODEL, NHEAD, D_FF, scale, vp(stream.cuda_stream))
         assert rc == 0
+
+    def step(i):   # on whatever stream is current (end-to-end loops)
+        run_on(i, torch.cuda.current_stream())
+
+    def fork():
+        for s_ in streams[1:]:
+            s_.wait_stream(main_stream)
+
+    def join():
+        for s_ in streams[1:]:
+            main_stream.wait_stream(s_)
+
+    def mstep(i):
+        run_on(i, streams[i % NS])
     with ClockSampler(0) as cs:
-        timed(step, max(args.warmup, 300))
-        ms = timed(step, args.steps)
+        timed(mstep, max(args.warmup, 300), join, fork)
+        ms = timed(mstep, args.steps, join, fork)
+        ms_one = timed(step, max(100, args.steps // 4)) if NS > 1 else ms
     hx = [torch.from_numpy(it.X).pin_memory() for it in insts]
     ho = [torch.empty_like(h).pin_memory() for h in hx]
     n_e2e = min(args.steps, 300)
@@ -285,8 +314,10 @@ def run_reference(args, rank):
     e2e_sync = BATCH / ((time.perf_counter() - t0) / n_e2e)
     e2e = BATCH / pipelined_e2e(torch, n_e2e, INSTANCES,
                                 lambda k: insts[k].x.copy_(hx[k], non_blocking=True), step,
-                                lambda k: ho[k].copy_(insts[k].out, non_blocking=True))
-    base.update({"value": BATCH / (ms * 1e-3), "ms_per_step": ms, "us_per_layer": ms * 1e3, "cpu_baseline": cpu,
+                                lambda k: ho[k].copy_(insts[k].out, non_blocking=True), depth=2 * NS,
+                                comp_streams=streams)
+    base.update({"value": BATCH / (ms * 1e-3), "ms_per_step": ms, "us_per_layer": ms_one * 1e3,
+                 "us_per_step_throughput": ms * 1e3, "batches_in_flight": NS, "cpu_baseline": cpu,
                  "reference_kind": "the reference's CUDA kernels (oracle/_ref): linears and LayerNorms once over all tokens, "
                                    "attention once per sequence, one stream, no host synchronisation",
                  "clocks": cs.summary(),
@@ -310,6 +341,8 @@ def main():
     ap.add_argument("--d-model", type=int, default=D_MODEL)
     ap.add_argument("--heads", type=int, default=NHEAD)
     ap.add_argument("--ff", type=int, default=D_FF)
+    ap.add_argument("--streams", type=int, default=4,
+                    help="independent batches in flight per GPU, one CUDA stream each (1 = one batch at a time)")
     ap.add_argument("--gather-every", type=int, default=4,
                     help="multi-GPU: output shards of this many steps travel in one all-gather (must divide the instance count)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -338,30 +371,53 @@ def main():
     pk = peaks()
     orc = oracle_lib.load()
     lens = [SEQ] * BATCH
-    # Output shards are gathered over NVLink with NCCL all-gathers issued asynchronously: the next steps' layers do
-    # not wait for them. The outputs of GE consecutive steps land side by side in one of three staging buffers and
-    # travel in one collective (every output row is gathered inside the timed region; fewer, larger collectives
-    # take fewer SMs away from the layer's kernels). At most 2 collectives are in flight, all are joined before
-    # the closing event of a timed region.
+    # Independent batches run concurrently, one CUDA stream each (step i on stream i mod NS): the layer's launches
+    # are short and seldom fill 148 SMs, so a second and third batch use what the first leaves idle.
+    NS = max(d for d in range(1, max(1, args.streams) + 1) if INSTANCES % d == 0)   # an instance stays on one stream
+    # None of them is the legacy default stream: the layer's CUDA-graph replay needs a capturable stream.
+    main_stream = torch.cuda.current_stream()
+    streams = [torch.cuda.Stream() for _ in range(NS)]
+    # Output shards are gathered over NVLink with NCCL all-gathers on a stream of their own: the next steps' layers
+    # do not wait for them. The outputs of GE consecutive steps land side by side in one of three staging buffers
+    # and travel in one collective (every output row is gathered inside the timed region; fewer, larger
+    # collectives take fewer SMs away from the layer's kernels). A staging buffer is written again only after the
+    # collective that read it has completed (events); everything is joined before the closing event of a timed
+    # region.
     GE = args.gather_every if world > 1 else 1
     if world > 1 and (GE < 1 or INSTANCES % GE or (INSTANCES // GE) % 3):
         GE = 1
     stage = [torch.zeros((GE * T, D_MODEL), dtype=torch.float16, device="cuda") for _ in range(3)] if world > 1 else None
     gathered = [torch.zeros((world * GE * T, D_MODEL), dtype=torch.float16, device="cuda") for _ in range(4)] if world > 1 else None
-    pending = collections.deque()
+    gstream = torch.cuda.Stream() if world > 1 else None
+    ev_step = [torch.cuda.Event() for _ in range(3 * GE)]   # step finished writing its slice of a staging buffer
+    ev_free = [torch.cuda.Event() for _ in range(3)]        # the collective that read a staging buffer has completed
+    gathers_issued = [0]
     open_group = [None]   # a group whose last step has not run yet
 
-    def gather(group):
-        pending.append(dist.all_gather_into_tensor(gathered[group % 4], stage[group % 3], async_op=True))
-        if len(pending) > 2:
-            pending.popleft().wait()
+    def gather(group, slots):
+        with torch.cuda.stream(gstream):
+            for sl in range(slots):
+                gstream.wait_event(ev_step[(group % 3) * GE + sl])
+            work = dist.all_gather_into_tensor(gathered[group % 4], stage[group % 3], async_op=True)
+            work.wait()                       # the gather stream waits for the collective, not the host
+            ev_free[group % 3].record(gstream)
+        gathers_issued[0] += 1
+
+    def fork():
+        for st in streams:
+            st.wait_stream(main_stream)
+        if gstream is not None:
+            gstream.wait_stream(main_stream)
 
     def join():
         if open_group[0] is not None:   # the step count was not a multiple of GE: gather the partial group too
-            gather(open_group[0])
+            g, slots = open_group[0]
+            gather(g, slots)
             open_group[0] = None
-        while pending:
-            pending.popleft().wait()
+        for st in streams:
+            main_stream.wait_stream(st)
+        if gstream is not None:
+            main_stream.wait_stream(gstream)
 
     class Instance:
         """One independent copy of the workload: its own weights, input, output and scratch."""
@@ -377,29 +433,46 @@ def main():
             self.scratch = torch.zeros(et.encoder_batch_buffer_size(et.KIND_TILE, D_MODEL, T, BATCH, SEQ, NHEAD) // 2,
                                        dtype=torch.float16, device="cuda")
 
-    def layer_step(insts):
+    lens_np = np.ascontiguousarray(lens, dtype=np.int32)
+    run_batch_c = et.lib().et_encoder_run_batch
+    vp = ctypes.c_void_p
+
+    def layer_step(insts, ns):
+        # The public C entry point, called with arguments converted once: instance k always runs on stream k mod ns
+        # and (multi-GPU) always writes the same slice of the same staging buffer, so the call is a constant.
+        calls = []
+        for k, it in enumerate(insts):
+            out = it.out if world == 1 else stage[(k // GE) % 3][(k % GE) * T:((k % GE) + 1) * T]
+            calls.append((it.enc._h, vp(out.data_ptr()), vp(it.x.data_ptr()), vp(lens_np.ctypes.data), vp(0), ctypes.c_int(BATCH),
+                          vp(it.scratch.data_ptr()), ctypes.c_size_t(it.scratch.numel() * 2),
+                          vp(streams[k % ns].cuda_stream)))
+
         def step(i):
-            it = insts[i % len(insts)]
+            k = i % len(insts)
+            st = streams[k % ns]
             if world > 1:
-                # with GE dividing the instance count (and the quotient a multiple of 3) an instance always writes
-                # to the same slice, so its replayed graph stays valid
                 group, slot = divmod(i, GE)
-                it.enc.run_batch(stage[group % 3][slot * T:(slot + 1) * T], it.x, lens, it.scratch)
-                open_group[0] = group
+                if group >= 3:
+                    st.wait_event(ev_free[group % 3])   # the collective of group - 3 has read this buffer
+            rc = run_batch_c(*calls[k])
+            if rc:
+                raise et.EtError(rc, et.lib().et_last_error().decode())
+            if world > 1:
+                ev_step[(group % 3) * GE + slot].record(st)
+            if world > 1:
+                open_group[0] = (group, slot + 1)
                 if slot == GE - 1:
-                    gather(group)
+                    gather(group, GE)
                     open_group[0] = None
-            else:
-                it.enc.run_batch(it.out, it.x, lens, it.scratch)
         return step
 
-    def measure(insts, steps, warmup):
-        step = layer_step(insts)
-        timed(step, 3 * len(insts), join)   # direct run, graph capture and first replay of every instance
-        timed(step, warmup, join)
+    def measure(insts, steps, warmup, ns=None):
+        step = layer_step(insts, NS if ns is None else ns)
+        timed(step, 3 * len(insts), join, fork)   # direct run, graph capture and first replay of every instance
+        timed(step, warmup, join, fork)
         if world > 1:
             dist.barrier()
-        ms = timed(step, steps, join)
+        ms = timed(step, steps, join, fork)
         if world > 1:
             dist.barrier()
             t = torch.tensor([ms], dtype=torch.float64, device="cuda")
@@ -412,6 +485,8 @@ def main():
     with ClockSampler(local_rank) as cs:
         ms = measure(insts, args.steps, args.warmup)
     clocks = cs.summary()
+    # one batch at a time (latency of a layer), measured beside the throughput figure
+    ms_one = measure(insts, max(300, args.steps // 4), 100, ns=1) if NS > 1 else ms
     value = BATCH * world / (ms * 1e-3)
     gemm_flops, attn_flops = layer_flops(lin)
 
@@ -422,11 +497,12 @@ def main():
 
     def e2e_step(i):
         it = insts[i % INSTANCES]
-        it.x.copy_(hx[i % INSTANCES], non_blocking=True)
-        it.enc.run_batch(it.out, it.x, lens, it.scratch)
-        if world > 1:
-            dist.all_gather_into_tensor(gathered[0][:world * T], it.out)
-        ho[i % INSTANCES].copy_(it.out, non_blocking=True)
+        with torch.cuda.stream(streams[0]):
+            it.x.copy_(hx[i % INSTANCES], non_blocking=True)
+            it.enc.run_batch(it.out, it.x, lens, it.scratch)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[0][:world * T], it.out)
+            ho[i % INSTANCES].copy_(it.out, non_blocking=True)
         torch.cuda.synchronize()          # the caller needs the result on the host before its next batch
     for i in range(INSTANCES):
         e2e_step(i)
@@ -445,7 +521,8 @@ def main():
     if world > 1:
         dist.barrier()
     e2e_s = pipelined_e2e(torch, n_e2e, INSTANCES, lambda k: insts[k].x.copy_(hx[k], non_blocking=True), e2e_compute,
-                          lambda k: ho[k].copy_(insts[k].out, non_blocking=True))
+                          lambda k: ho[k].copy_(insts[k].out, non_blocking=True), depth=2 * NS,
+                          comp_streams=streams if world == 1 else None)
     if world > 1:
         t = torch.tensor([e2e_s, e2e_sync_s], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -488,7 +565,8 @@ def main():
                         "per-CTA latency (prologue, slot-ring hops, epilogue), see DESIGN.md"}
 
     result = {"metric": METRIC, "value": value, "unit": "sequences/s", "n_gpus": world, "steps": args.steps,
-              "warmup": args.warmup, "ms_per_step": ms, "us_per_layer": ms * 1e3, "higher_is_better": True,
+              "warmup": args.warmup, "ms_per_step": ms, "us_per_layer": ms_one * 1e3,
+              "us_per_step_throughput": ms * 1e3, "batches_in_flight": NS, "higher_is_better": True,
               "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
               "config": workload_config(args), "clocks": clocks, "e2e": e2e, "gpu_launches": 7 * args.steps,
               "launches_per_step": "7: fused Q|K|V tile GEMM, attention, output tile GEMM, LayerNorm, FFN1 tile GEMM (GELU), "
@@ -499,11 +577,11 @@ def main():
         sweep = {}
         for s in SWEEP:
             if abs(s - args.sparsity) < 1e-9:
-                sweep[str(s)] = {"us_per_layer": ms * 1e3, "sequences_per_s": BATCH / (ms * 1e-3)}
+                sweep[str(s)] = {"us_per_step": ms * 1e3, "sequences_per_s": BATCH / (ms * 1e-3)}
                 continue
             i2 = [Instance(s, i) for i in range(INSTANCES)]
             m2 = measure(i2, max(300, args.steps // 4), 100)
-            sweep[str(s)] = {"us_per_layer": m2 * 1e3, "sequences_per_s": BATCH / (m2 * 1e-3)}
+            sweep[str(s)] = {"us_per_step": m2 * 1e3, "sequences_per_s": BATCH / (m2 * 1e-3)}
             del i2
         result["sweep"] = sweep
         # bandwidth kernels on inputs larger than L2
