@@ -129,6 +129,39 @@ void row_spmm_cache_clear() {
 // ------------------------------------------------------------------------------ encoder layer
 enum EncoderKind { kTile = 0, kPrune = 1, kLength = 2, kPruneQKV = 3 };
 
+// The legacy default stream cannot be captured, so a layer launched there could not be replayed as a CUDA graph
+// (and its seven launches would cost the host three times as much). Calls on the legacy stream therefore run on a
+// stream of the object, ordered behind the caller's stream by one event and ahead of it by another.
+struct StreamBridge {
+    cudaStream_t own = nullptr;
+    cudaEvent_t in = nullptr, out = nullptr;
+    ~StreamBridge() {
+        if (in) cudaEventDestroy(in);
+        if (out) cudaEventDestroy(out);
+        if (own) cudaStreamDestroy(own);
+    }
+    static bool is_legacy(cudaStream_t st) { return st == nullptr || st == cudaStreamLegacy; }
+    // Returns the stream to run on, or nullptr if the bridge could not be set up (the caller then stays on `st`).
+    cudaStream_t begin(cudaStream_t st) {
+        if (!own) {
+            if (cudaStreamCreateWithFlags(&own, cudaStreamNonBlocking) != cudaSuccess ||
+                cudaEventCreateWithFlags(&in, cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&out, cudaEventDisableTiming) != cudaSuccess) {
+                cudaGetLastError();
+                return nullptr;
+            }
+        }
+        if (cudaEventRecord(in, st) != cudaSuccess || cudaStreamWaitEvent(own, in, 0) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        return own;
+    }
+    void end(cudaStream_t st) {
+        if (cudaEventRecord(out, own) != cudaSuccess || cudaStreamWaitEvent(st, out, 0) != cudaSuccess) cudaGetLastError();
+    }
+};
+
 struct Encoder {
     int kind = kTile, d_model = 0, seq_len = 0, nheads = 0, d_ff = 0;
     half* buffer = nullptr;  // caller-owned scratch for run(): buffer_num * seq_len * d_model halfs (+ scores)
@@ -148,6 +181,7 @@ struct Encoder {
     };
     std::vector<Replay> replays;
     bool use_graphs = true;
+    StreamBridge bridge;
     ~Encoder() {
         for (auto& r : replays)
             if (r.exec) cudaGraphExecDestroy(r.exec);
@@ -243,6 +277,7 @@ struct Model {
     };
     std::vector<Replay> replays;
     bool use_graphs = true;
+    StreamBridge bridge;
     void drop_replays() {
         for (auto& r : replays)
             if (r.exec) cudaGraphExecDestroy(r.exec);
@@ -512,6 +547,15 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (batch == 0) return ET_OK;
     ET_REQUIRE(seq_lens_host, "et_encoder_run_batch: null seq_lens");
+    if (e->use_graphs && et::StreamBridge::is_legacy(st)) {
+        // the legacy default stream cannot be captured: run on the encoder's own stream, ordered by events
+        cudaStream_t own = e->bridge.begin(st);
+        if (own) {
+            const int rc = et_encoder_run_batch(enc, out, in, seq_lens_host, valid_lens_host, batch, scratch, scratch_bytes, own);
+            e->bridge.end(st);
+            return rc;
+        }
+    }
     std::vector<int> meta(2 * batch + 1);
     meta[0] = 0;
     bool uniform = true;
@@ -665,6 +709,15 @@ int et_model_run_batch(et_model* model, void* out, const void* in, const int* se
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (batch == 0) return ET_OK;
     ET_REQUIRE(seq_lens_host, "et_model_run_batch: null seq_lens");
+    if (m->use_graphs && et::StreamBridge::is_legacy(st)) {
+        // the legacy default stream cannot be captured: run on the model's own stream, ordered by events
+        cudaStream_t own = m->bridge.begin(st);
+        if (own) {
+            const int rc = et_model_run_batch(model, out, in, seq_lens_host, valid_lens_host, batch, own);
+            m->bridge.end(st);
+            return rc;
+        }
+    }
     std::vector<int> meta(2 * batch + 1);
     meta[0] = 0;
     bool uniform = true;

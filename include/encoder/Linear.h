@@ -30,11 +30,11 @@ class Linear_tile {
     ~Linear_tile() { et_tile_weight_destroy(handle_); }
 
     void run(half* out, half* in, cudaStream_t stream) {
-        et_shim::require_ok(et_tile_linear(handle_, out, in, size, is_gelu ? 1 : 0, stream), "Linear_tile::run");
+        et_shim::require_ok(et_tile_linear(handle_, out, in, size, is_gelu ? 1 : 0, et_shim::stream_of(stream)), "Linear_tile::run");
     }
     // Extension: any token count (packed batch).
     void run(half* out, half* in, int tokens, cudaStream_t stream) {
-        et_shim::require_ok(et_tile_linear(handle_, out, in, tokens, is_gelu ? 1 : 0, stream), "Linear_tile::run");
+        et_shim::require_ok(et_tile_linear(handle_, out, in, tokens, is_gelu ? 1 : 0, et_shim::stream_of(stream)), "Linear_tile::run");
     }
     et_tile_weight* handle() { return handle_; }
 };
@@ -78,10 +78,10 @@ class Linear_row {
 
     // The handle selects nothing here (no cuBLAS); the work goes to the default stream.
     void run(half* out, half* in, cublasHandle_t /*handle*/) {
-        et_shim::require_ok(et_row_linear(handle_, out, in, size, nullptr), "Linear_row::run");
+        et_shim::require_ok(et_row_linear(handle_, out, in, size, et_shim::stream_of(nullptr)), "Linear_row::run");
     }
     void run(half* out, half* in, int tokens, cudaStream_t stream) {
-        et_shim::require_ok(et_row_linear(handle_, out, in, tokens, stream), "Linear_row::run");
+        et_shim::require_ok(et_row_linear(handle_, out, in, tokens, et_shim::stream_of(stream)), "Linear_row::run");
     }
     et_row_weight* handle() { return handle_; }
 };

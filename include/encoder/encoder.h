@@ -26,14 +26,14 @@ class Encoder_base {
 
     // One sequence of seq_len tokens; out may alias in. Runs on the default stream without host synchronisation.
     virtual void run(half* out, half* in) {
-        et_shim::require_ok(et_encoder_run(enc_, out, in, nullptr), "Encoder::run");
+        et_shim::require_ok(et_encoder_run(enc_, out, in, et_shim::stream_of(nullptr)), "Encoder::run");
     }
     // Extension: `batch` packed sequences of seq_lens[b] tokens each (host array); scratch is a device buffer
     // of batch_buffer_size(...) bytes.
     void run_batch(half* out, half* in, const int* seq_lens, int batch, void* scratch, size_t scratch_bytes,
                    cudaStream_t stream = nullptr, const int* valid_lens = nullptr) {
         et_shim::require_ok(et_encoder_run_batch(enc_, out, in, seq_lens, valid_lens, batch, scratch, scratch_bytes,
-                                                 stream),
+                                                 et_shim::stream_of(stream)),
                             "Encoder::run_batch");
     }
     static size_t buffer_size(int d_model_, int seq_len_, int nheads_) {
@@ -133,7 +133,7 @@ class Encoder_stack {
     void run_batch(half* out, half* in, const int* seq_lens, int batch, cudaStream_t stream = nullptr,
                    const int* valid_lens = nullptr) {
         if (!model_) et_shim::require_ok(et_model_create(&model_, pending_.data(), (int)pending_.size()), "Encoder_stack");
-        et_shim::require_ok(et_model_run_batch(model_, out, in, seq_lens, valid_lens, batch, stream),
+        et_shim::require_ok(et_model_run_batch(model_, out, in, seq_lens, valid_lens, batch, et_shim::stream_of(stream)),
                             "Encoder_stack::run_batch");
     }
     void reserve(int total_tokens, int batch, int max_len) {

@@ -8,6 +8,7 @@
 #define cudaChk(call) ::et_shim::cuda_check((call), __FILE__, __LINE__)
 
 namespace et_shim {
+
 inline void cuda_check(cudaError_t status, const char* file, int line) {
     if (status == cudaSuccess) return;
     std::fprintf(stderr, "CUDA Error: %s %s %d\n", cudaGetErrorString(status), file, line);

@@ -26,6 +26,16 @@ typedef int cublasGemmAlgo_t;
 #endif
 
 namespace et_shim {
+// A null stream means the default stream of the CALLER's translation unit: the per-thread one when the caller is
+// compiled with --default-stream per-thread (as the reference is, CMakeLists.txt:13), else the legacy one. The
+// library itself is compiled without that flag, so the choice has to be made here, in the caller's code.
+inline cudaStream_t stream_of(cudaStream_t s) {
+#ifdef CUDA_API_PER_THREAD_DEFAULT_STREAM
+    return s ? s : cudaStreamPerThread;
+#else
+    return s;
+#endif
+}
 inline void require_ok(int status, const char* what) {
     if (status != ET_OK) {
         std::fprintf(stderr, "%s failed (%d): %s\n", what, status, et_last_error());
@@ -36,26 +46,26 @@ inline void require_ok(int status, const char* what) {
 
 inline void skip_layernorm_kernelLauncher(half* in_out, const half* skip, const half* gamma, const half* beta,
                                           int num, int size, cudaStream_t stream) {
-    et_shim::require_ok(et_skip_layernorm(in_out, skip, gamma, beta, num, size, stream), "skip_layernorm");
+    et_shim::require_ok(et_skip_layernorm(in_out, skip, gamma, beta, num, size, et_shim::stream_of(stream)), "skip_layernorm");
 }
 
 // The handle's stream is not consulted (no cuBLAS here): the work goes to the default stream, which is the
 // per-thread stream under --default-stream per-thread as in the reference build.
 inline void row_spmm_add_bias_kernelLauncher(half* out, const half* in, const half* weight, const half* bias, int M,
                                              int N, int K, cublasHandle_t /*handle*/, cublasGemmAlgo_t /*algo*/) {
-    et_shim::require_ok(et_row_spmm_bias(out, in, weight, bias, M, N, K, nullptr), "row_spmm_add_bias");
+    et_shim::require_ok(et_row_spmm_bias(out, in, weight, bias, M, N, K, et_shim::stream_of(nullptr)), "row_spmm_add_bias");
 }
 
 // With an explicit K (row pitch of X = in_feat).
 inline void tile_spmm_add_bias_kernelLauncher(half* Y, half* X, int* W_row_ptr, int* W_row_offset, half* W_data,
                                               int M, int N, int K, half* bias, cudaStream_t stream) {
-    et_shim::require_ok(et_tile_spmm_bias(Y, X, W_row_ptr, W_row_offset, W_data, M, N, K, bias, 0, stream),
+    et_shim::require_ok(et_tile_spmm_bias(Y, X, W_row_ptr, W_row_offset, W_data, M, N, K, bias, 0, et_shim::stream_of(stream)),
                         "tile_spmm_add_bias");
 }
 inline void tile_spmm_add_bias_gelu_kernelLauncher(half* Y, half* X, int* W_row_ptr, int* W_row_offset,
                                                    half* W_data, int M, int N, int K, half* bias,
                                                    cudaStream_t stream) {
-    et_shim::require_ok(et_tile_spmm_bias(Y, X, W_row_ptr, W_row_offset, W_data, M, N, K, bias, 1, stream),
+    et_shim::require_ok(et_tile_spmm_bias(Y, X, W_row_ptr, W_row_offset, W_data, M, N, K, bias, 1, et_shim::stream_of(stream)),
                         "tile_spmm_add_bias_gelu");
 }
 // The reference's 9-argument form has no K and reads X with pitch M; it is only meaningful when the token
@@ -71,19 +81,19 @@ inline void tile_spmm_add_bias_gelu_kernelLauncher(half* Y, half* X, int* W_row_
 
 inline void OTF_attention_kernelLauncher(half* out, half* Q, half* K, half* V, half* mask, int seq_len, int d_model,
                                          int nhead, cudaStream_t stream) {
-    et_shim::require_ok(et_attention_otf(out, Q, K, V, mask, seq_len, d_model, nhead, stream), "OTF_attention");
+    et_shim::require_ok(et_attention_otf(out, Q, K, V, mask, seq_len, d_model, nhead, et_shim::stream_of(stream)), "OTF_attention");
 }
 
 inline void Prune_attention_kernelLauncher(half* out, half* Q, half* K, half* V, int* v_col_id, int* v_head_ptr,
                                            int nnz_col_v, half* mask, int seq_len, int d_model, int nhead,
                                            cudaStream_t stream = nullptr) {
     et_shim::require_ok(et_attention_prune(out, Q, K, V, v_col_id, v_head_ptr, nnz_col_v, mask, seq_len, d_model,
-                                           nhead, stream),
+                                           nhead, et_shim::stream_of(stream)),
                         "Prune_attention");
 }
 
 inline void sharedQK_attention_kernelLauncher(half* out, half* QK, half* V, half* mask, int seq_len, int d_model,
                                               int nhead, cudaStream_t stream = nullptr) {
-    et_shim::require_ok(et_attention_sharedqk(out, QK, V, mask, seq_len, d_model, nhead, stream),
+    et_shim::require_ok(et_attention_sharedqk(out, QK, V, mask, seq_len, d_model, nhead, et_shim::stream_of(stream)),
                         "sharedQK_attention");
 }

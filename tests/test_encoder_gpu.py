@@ -204,3 +204,27 @@ def test_encoder_rejects_bad_arguments(et, orc):
         enc.run_batch(x, x, [-1], small)
     with pytest.raises(et.EtError):
         enc.set_materialize_scores(True)  # only the length encoder has that path
+
+
+def test_run_batch_on_the_legacy_stream_and_on_a_side_stream_agree(et, orc):
+    """On the legacy default stream the layer runs on a stream of the encoder (ordered by events) so that the graph
+    replay still engages; results are bit-identical to a caller-provided stream, and ordered with the caller's
+    other work on the legacy stream."""
+    d, H, dff, B, S = 256, 4, 512, 3, 64
+    lin, ln = make_layer(orc, d, dff, 0.5, seed=61)
+    enc = build_encoder(et, et.KIND_TILE, lin, ln, d, S, H, B * S)
+    scratch = torch.zeros(et.encoder_batch_buffer_size(et.KIND_TILE, d, B * S, B, S, H) // 2, dtype=torch.float16, device="cuda")
+    x = dev(util.activations(62, (B * S, d)))
+    side = torch.cuda.Stream()
+    ref_out = torch.zeros_like(x)
+    with torch.cuda.stream(side):
+        enc.run_batch(ref_out, x, [S] * B, scratch)
+    side.synchronize()
+    for call in range(4):            # direct, captured, replayed, replayed
+        xin = x.clone()              # produced on the legacy stream right before the call
+        out = torch.zeros_like(x)
+        enc.run_batch(out, xin, [S] * B, scratch)
+        doubled = out * 2            # consumed on the legacy stream right after the call
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref_out), f"call {call}"
+        assert torch.equal(doubled, ref_out * 2)
