@@ -59,6 +59,12 @@ extern "C" int et_tile_spmm_cache_clear(void) {
     return ET_OK;
 }
 
+extern "C" int et_set_tuning_goal(int goal) {
+    if (goal != 0 && goal != 1) return et::fail(ET_ERR_INVALID, "et_set_tuning_goal: goal must be 0 (latency) or 1 (throughput)");
+    et::tile_gemm_set_goal(goal);
+    return ET_OK;
+}
+
 // Not part of the public header: used by profiling builds of the library only.
 extern "C" int et_debug_set_gemm_profile_buffer(void* dev_buf) {
     et::tile_gemm_set_profile_buffer(static_cast<long long*>(dev_buf));

@@ -514,6 +514,12 @@ static RingShape ring_shape(int nb, int stage_b_bytes) {
 // Block-rows per CTA from a model of the persistent kernel: a chunk takes the ring period, or its UMMAs (~10
 // clocks each with eight issuing warps), or its share of L2 bandwidth (~64 bytes per clock per SM), whichever
 // is longest; a tile ends with an epilogue of ~350 clocks per 32 columns and warp.
+// What the pack optimises: 0 = the duration of one launch on an otherwise idle GPU (tiles spread over as many SMs
+// as possible), 1 = SM time per launch (fewer, larger tiles: the right choice when several independent batches
+// are in flight on separate streams and keep all SMs busy anyway).
+static int g_goal = 0;
+void tile_gemm_set_goal(int goal) { g_goal = goal == 1 ? 1 : 0; }
+
 static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double density) {
     const int slabs = std::max(1, (size_hint + kSlab - 1) / kSlab);
     const int sms = std::max(1, sm_count());
@@ -535,7 +541,7 @@ static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double densi
         const double t_chunk = std::max({rs.period, 10.0 * tiles_per_chunk,
                                          (kXStageBytes + tiles_per_chunk * 528.0) / 64.0});
         const double t_tile = k_chunks * t_chunk + 350.0 * ((nbe + 3) / 4) + 800.0;
-        const double cost = per_cta * t_tile + 3000.0;
+        const double cost = g_goal == 1 ? (double)tiles * t_tile : per_cta * t_tile + 3000.0;
         if (best_nb == 0 || cost < best * 0.999) { best = cost; best_nb = nbe; }
     }
     return best_nb > 0 ? best_nb : std::min(8, std::max(n_block_rows, 1));

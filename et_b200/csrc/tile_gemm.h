@@ -26,4 +26,8 @@ void tile_spmm_cache_clear();
 // Profiling builds (-DET_GEMM_PROFILE): device buffer of >= 1024 clock64 stamps written by CTA (0,0).
 void tile_gemm_set_profile_buffer(long long* dev_buf);
 
+// 0: shortest single launch (default); 1: least SM time per launch (several batches in flight). Applies to weights
+// packed afterwards.
+void tile_gemm_set_goal(int goal);
+
 }  // namespace et

@@ -14,7 +14,7 @@ __all__ = [
     "RowWeight", "attention_otf", "attention_prune", "qk_scores", "attention_sharedqk", "attention_batch", "attention_static_scores",
     "gen_sparse_tile_mat", "gen_sparse_row_mat", "build_head_ptr", "Encoder", "encoder_buffer_size",
     "encoder_batch_buffer_size", "KIND_TILE", "KIND_PRUNE", "KIND_LENGTH", "KIND_PRUNE_QKV",
-    "Model", "prune_dense_to_tiles", "select_rows_magnitude", "compact_rows",
+    "Model", "prune_dense_to_tiles", "select_rows_magnitude", "compact_rows", "set_tuning_goal",
 ]
 
 _i = ctypes.c_int
@@ -35,6 +35,12 @@ def softmax_mask(scores, mask=None, valid_len=None, stream=None):
     check(lib().et_softmax_mask(ptr(scores), ptr(mask), _i(nmat), _i(L),
                                 _i(L if valid_len is None else valid_len), stream_ptr(stream)))
     return scores
+
+
+def set_tuning_goal(goal):
+    """"latency" (default): weights created afterwards are packed for the shortest single launch; "throughput": for
+    the least SM time per launch (several independent batches in flight on separate streams)."""
+    check(lib().et_set_tuning_goal(_i({"latency": 0, "throughput": 1}[goal])))
 
 
 class TileWeight:

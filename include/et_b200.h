@@ -59,6 +59,13 @@ int et_tile_linear(const et_tile_weight* w, void* Y, const void* X, int tokens, 
 /* Reads and clears the weight's device error word (synchronises): ET_ERR_DEVICE_TIMEOUT and the
  * code in *code when a bounded wait inside the kernel gave up since the last check. */
 int et_tile_weight_check(const et_tile_weight* w, int* code);
+/* Extension (no counterpart in the reference): what weights created AFTERWARDS are packed for. 0 (default): the
+ * shortest duration of one launch on an otherwise idle GPU (tiles spread over as many SMs as possible). 1: the
+ * least SM time per launch (fewer, larger tiles), for callers that keep several independent batches in flight on
+ * separate streams, where all SMs are busy anyway. Process-wide. */
+#define ET_GOAL_LATENCY 0
+#define ET_GOAL_THROUGHPUT 1
+int et_set_tuning_goal(int goal);
 /* info[6] = {block_rows_per_cta, n_chunks, k_chunks, stages, stage_bytes, packed_bytes}. */
 int et_tile_weight_info(const et_tile_weight* w, int* info);
 /* Same contraction from DEVICE-resident tile arrays, K = in_feat explicit. The packed form of a
