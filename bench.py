@@ -175,41 +175,61 @@ def timed(step, steps, finish=None, start=None):
     return e0.elapsed_time(e1) / steps
 
 
-def pipelined_e2e(torch, n_steps, n_inst, h2d, compute, d2h, depth=4, comp_streams=None):
+def pipelined_e2e(torch, n_steps, n_inst, h2d, compute, d2h, depth, comp_streams):
     """Seconds per step of a three-stage pipeline over `n_inst` independent buffer sets: the host-to-device copy of
-    step i+1 and the device-to-host copy of step i-1 run on their own streams under the layer of step i. Every
-    step's input is copied from pinned host memory and its result is copied back inside the timed region; the host
-    waits for the result of step i-depth before it enqueues step i (a server consuming results, and a bound on
-    the work in flight)."""
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    comps = comp_streams or [torch.cuda.current_stream()]   # set k always computes on stream k mod len(comps)
-    ev_in = [torch.cuda.Event() for _ in range(n_inst)]
-    ev_comp = [torch.cuda.Event() for _ in range(n_inst)]
-    ev_out = [torch.cuda.Event() for _ in range(n_inst)]
+    step i+1 and the device-to-host copy of step i-1 run on their own streams under the layers of the steps in
+    between (set k always computes on comp_streams[k mod len]). Every step's input is copied from pinned host
+    memory and its result is copied back inside the timed region; the host waits for the result of step i-depth
+    before it enqueues step i (a server consuming results, and a bound on the work in flight).
+
+    h2d[k] / d2h[k] = (dst pointer, src pointer, bytes); compute(k) launches set k's layer on its stream. Copies
+    and events go through the CUDA runtime directly (ctypes): the host's enqueue cost per step would otherwise
+    exceed the device time of a step."""
+    rt = ctypes.CDLL("libcudart.so.12")
+    vp, sz = ctypes.c_void_p, ctypes.c_size_t
+    rt.cudaMemcpyAsync.argtypes = [vp, vp, sz, ctypes.c_int, vp]
+    rt.cudaEventRecord.argtypes = [vp, vp]
+    rt.cudaStreamWaitEvent.argtypes = [vp, vp, ctypes.c_uint]
+    rt.cudaEventSynchronize.argtypes = [vp]
+    rt.cudaEventCreateWithFlags.argtypes = [ctypes.POINTER(vp), ctypes.c_uint]
+    rt.cudaEventDestroy.argtypes = [vp]
+
+    def chk(rc):
+        if rc != 0:
+            raise RuntimeError(f"CUDA runtime call failed with error {rc}")
+
+    def new_event():
+        ev = vp()
+        chk(rt.cudaEventCreateWithFlags(ctypes.byref(ev), 2))   # cudaEventDisableTiming
+        return ev
+    t_in, t_out = torch.cuda.Stream(), torch.cuda.Stream()
+    s_in, s_out = vp(t_in.cuda_stream), vp(t_out.cuda_stream)
+    comps = [vp(st.cuda_stream) for st in comp_streams]
+    ev_in = [new_event() for _ in range(n_inst)]
+    ev_comp = [new_event() for _ in range(n_inst)]
+    ev_out = [new_event() for _ in range(n_inst)]
     used = [False] * n_inst
 
     def step(i):
         k = i % n_inst
         if i >= depth and used[(i - depth) % n_inst]:
-            ev_out[(i - depth) % n_inst].synchronize()
-        with torch.cuda.stream(s_in):
-            if used[k]:
-                s_in.wait_event(ev_comp[k])    # the previous layer on this set has read its input
-            h2d(k)
-            ev_in[k].record(s_in)
-        s_comp = comps[k % len(comps)]
-        s_comp.wait_event(ev_in[k])
+            chk(rt.cudaEventSynchronize(ev_out[(i - depth) % n_inst]))
         if used[k]:
-            s_comp.wait_event(ev_out[k])       # the previous result has left the output buffer
-        with torch.cuda.stream(s_comp):
-            compute(k)
-        ev_comp[k].record(s_comp)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(ev_comp[k])
-            d2h(k)
-            ev_out[k].record(s_out)
+            chk(rt.cudaStreamWaitEvent(s_in, ev_comp[k], 0))    # the previous layer on this set has read its input
+        chk(rt.cudaMemcpyAsync(h2d[k][0], h2d[k][1], h2d[k][2], 1, s_in))
+        chk(rt.cudaEventRecord(ev_in[k], s_in))
+        s_comp = comps[k % len(comps)]
+        chk(rt.cudaStreamWaitEvent(s_comp, ev_in[k], 0))
+        if used[k]:
+            chk(rt.cudaStreamWaitEvent(s_comp, ev_out[k], 0))   # the previous result has left the output buffer
+        compute(k)
+        chk(rt.cudaEventRecord(ev_comp[k], s_comp))
+        chk(rt.cudaStreamWaitEvent(s_out, ev_comp[k], 0))
+        chk(rt.cudaMemcpyAsync(d2h[k][0], d2h[k][1], d2h[k][2], 2, s_out))
+        chk(rt.cudaEventRecord(ev_out[k], s_out))
         used[k] = True
 
+    torch.cuda.synchronize()
     for i in range(2 * n_inst):
         step(i)
     torch.cuda.synchronize()
@@ -217,7 +237,10 @@ def pipelined_e2e(torch, n_steps, n_inst, h2d, compute, d2h, depth=4, comp_strea
     for i in range(n_steps):
         step(i)
     torch.cuda.synchronize()
-    return (time.perf_counter() - t0) / n_steps
+    dt = (time.perf_counter() - t0) / n_steps
+    for ev in ev_in + ev_comp + ev_out:
+        rt.cudaEventDestroy(ev)
+    return dt
 
 
 def run_reference(args, rank):
@@ -313,10 +336,12 @@ def run_reference(args, rank):
     for i in range(n_e2e):
         e2e_step(i)
     e2e_sync = BATCH / ((time.perf_counter() - t0) / n_e2e)
+    nbytes = hx[0].numel() * 2
     e2e = BATCH / pipelined_e2e(torch, n_e2e, INSTANCES,
-                                lambda k: insts[k].x.copy_(hx[k], non_blocking=True), step,
-                                lambda k: ho[k].copy_(insts[k].out, non_blocking=True), depth=2 * NS,
-                                comp_streams=streams)
+                                [(vp(insts[k].x.data_ptr()), vp(hx[k].data_ptr()), nbytes) for k in range(INSTANCES)],
+                                lambda k: run_on(k, streams[k % NS]),
+                                [(vp(ho[k].data_ptr()), vp(insts[k].out.data_ptr()), nbytes) for k in range(INSTANCES)],
+                                depth=2 * NS, comp_streams=streams)
     base.update({"value": BATCH / (ms * 1e-3), "ms_per_step": ms, "us_per_layer": ms_one * 1e3,
                  "us_per_step_throughput": ms * 1e3, "batches_in_flight": NS, "cpu_baseline": cpu,
                  "reference_kind": "the reference's CUDA kernels (oracle/_ref): linears and LayerNorms once over all tokens, "
@@ -523,16 +548,24 @@ def main():
         e2e_step(i)
     e2e_sync_s = (time.perf_counter() - t0) / n_e2e
 
+    e2e_calls = [(it.enc._h, vp(it.out.data_ptr()), vp(it.x.data_ptr()), vp(lens_np.ctypes.data), vp(0), ctypes.c_int(BATCH),
+                  vp(it.scratch.data_ptr()), ctypes.c_size_t(it.scratch.numel() * 2), vp(streams[k % NS].cuda_stream))
+                 for k, it in enumerate(insts)]
+
     def e2e_compute(k):
-        it = insts[k]
-        it.enc.run_batch(it.out, it.x, lens, it.scratch)
+        rc = run_batch_c(*e2e_calls[k])
+        if rc:
+            raise et.EtError(rc, et.lib().et_last_error().decode())
         if world > 1:
-            dist.all_gather_into_tensor(gathered[0][:world * T], it.out)
+            with torch.cuda.stream(streams[k % NS]):
+                dist.all_gather_into_tensor(gathered[0][:world * T], insts[k].out)
     if world > 1:
         dist.barrier()
-    e2e_s = pipelined_e2e(torch, n_e2e, INSTANCES, lambda k: insts[k].x.copy_(hx[k], non_blocking=True), e2e_compute,
-                          lambda k: ho[k].copy_(insts[k].out, non_blocking=True), depth=2 * NS,
-                          comp_streams=streams if world == 1 else None)
+    nbytes = hx[0].numel() * 2
+    e2e_s = pipelined_e2e(torch, n_e2e, INSTANCES,
+                          [(vp(insts[k].x.data_ptr()), vp(hx[k].data_ptr()), nbytes) for k in range(INSTANCES)], e2e_compute,
+                          [(vp(ho[k].data_ptr()), vp(insts[k].out.data_ptr()), nbytes) for k in range(INSTANCES)],
+                          depth=2 * NS, comp_streams=streams)
     if world > 1:
         t = torch.tensor([e2e_s, e2e_sync_s], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
