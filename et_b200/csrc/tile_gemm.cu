@@ -204,7 +204,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const uint32_t a_col0 = 512u - (uint32_t)(RA * kSlotCols);
     const int my_tiles = (p.n_tiles - (int)blockIdx.x + G - 1) / G;
     if (tid == 0) ET_STAMP(0);
-    pdl_launch_dependents();   // the next kernel may set itself up on idle SMs while this one runs
+    // The next kernel in the stream is released late, when this CTA's last main loop is over: a dependent CTA
+    // that becomes resident earlier would hold an SM while it waits for this whole grid, an SM that a kernel of
+    // another stream (another batch in flight) could use.
 
     if (warp == 0) {
         // ---------------- producer warp: lane 0 issues the copies, lane 1 polls (a wait by the thread that has
@@ -421,6 +423,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     }
                 }
                 tc_fence_after();
+                if (tl + 1 == my_tiles) pdl_launch_dependents();   // its set-up overlaps this last epilogue
                 if (w == 0 && lane == 0 && tl < 16) ET_STAMP(1400 + tl * 16);
                 const int units = (p.nb + 1) >> 1;
                 const bool more = tl + 1 < my_tiles;
