@@ -483,6 +483,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 
 struct TileWeight {
     int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, stages = 0, a_slots = 0, epi_bufs = 1;
+    int tiles_per_cta = 1;   // > 1 when packed for SM time: a CTA takes that many tiles even when SMs are free
     long ntile = 0;
     int size_hint = 0;
     // the caller's arrays, kept so that weights can be concatenated (Q|K|V in one launch) and re-packed
@@ -522,6 +523,7 @@ static RingShape ring_shape(int nb, int stage_b_bytes) {
 // as possible), 1 = SM time per launch (fewer, larger tiles: the right choice when several independent batches
 // are in flight on separate streams and keep all SMs busy anyway).
 static int g_goal = 0;
+constexpr int kThroughputTilesPerCta = 2;
 void tile_gemm_set_goal(int goal) { g_goal = goal == 1 ? 1 : 0; }
 
 static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double density) {
@@ -566,6 +568,7 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
 
     auto* w = new TileWeight();
     w->K = K; w->N = N; w->ntile = ntile; w->size_hint = size_hint;
+    w->tiles_per_cta = g_tune[2] > 0 ? g_tune[2] : (g_goal == 1 ? kThroughputTilesPerCta : 1);
     const double density = (double)ntile / std::max(1.0, (double)NBR * (K / 16));
     w->nb = choose_nb(NBR, (K + kKC - 1) / kKC, size_hint, density);
     if (nb_override <= 0 && g_tune[0] > 0) nb_override = g_tune[0];
@@ -715,7 +718,9 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     for (size_t c = 0; c < w->h_first.size(); ++c) p.first[c] = w->h_first[c];
     const size_t smem = (size_t)w->stages * (kXStageBytes + w->stage_b_bytes) +
                         (size_t)w->epi_bufs * kIssuers * kUnitBytes + sizeof(Shared) + 1024;
-    dim3 grid(std::min(p.n_tiles, sm_count()));
+    // Packed for SM time (several batches in flight): a CTA takes several tiles in a row even when SMs are free,
+    // so that set-up and pipeline fill are paid once and the next tile's loads run under an epilogue.
+    dim3 grid(std::min((p.n_tiles + w->tiles_per_cta - 1) / w->tiles_per_cta, sm_count()));
     const cudaError_t le = gelu ? launch_pdl(tile_gemm_kernel<true>, grid, dim3(kThreads), smem, st, tm, tmy, p)
                                 : launch_pdl(tile_gemm_kernel<false>, grid, dim3(kThreads), smem, st, tm, tmy, p);
     if (le != cudaSuccess) return cuda_status(le, "tile linear launch");
