@@ -369,7 +369,7 @@ def main():
     ap.add_argument("--ff", type=int, default=D_FF)
     ap.add_argument("--streams", type=int, default=6,
                     help="independent batches in flight per GPU, one CUDA stream each (1 = one batch at a time)")
-    ap.add_argument("--gather-every", type=int, default=4,
+    ap.add_argument("--gather-every", type=int, default=12,
                     help="multi-GPU: output shards of this many steps travel in one all-gather (must divide the instance count)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the sweep and the LayerNorm/softmax bandwidth legs")
@@ -410,7 +410,7 @@ def main():
     # collective that read it has completed (events); everything is joined before the closing event of a timed
     # region.
     GE = args.gather_every if world > 1 else 1
-    if world > 1 and (GE < 1 or INSTANCES % GE or (INSTANCES // GE) % 3):
+    if world > 1 and (GE < 1 or INSTANCES % GE):
         GE = 1
     stage = [torch.zeros((GE * T, D_MODEL), dtype=torch.float16, device="cuda") for _ in range(3)] if world > 1 else None
     gathered = [torch.zeros((world * GE * T, D_MODEL), dtype=torch.float16, device="cuda") for _ in range(4)] if world > 1 else None
@@ -465,13 +465,17 @@ def main():
 
     def layer_step(insts, ns):
         # The public C entry point, called with arguments converted once: instance k always runs on stream k mod ns
-        # and (multi-GPU) always writes the same slice of the same staging buffer, so the call is a constant.
+        # and (multi-GPU) always writes slice k mod GE of a staging buffer, so there is one constant call per
+        # (staging buffer, instance); the layer keeps one replayable graph per output address.
         calls = []
-        for k, it in enumerate(insts):
-            out = it.out if world == 1 else stage[(k // GE) % 3][(k % GE) * T:((k % GE) + 1) * T]
-            calls.append((it.enc._h, vp(out.data_ptr()), vp(it.x.data_ptr()), vp(lens_np.ctypes.data), vp(0), ctypes.c_int(BATCH),
-                          vp(it.scratch.data_ptr()), ctypes.c_size_t(it.scratch.numel() * 2),
-                          vp(streams[k % ns].cuda_stream)))
+        for b in range(3 if world > 1 else 1):
+            row = []
+            for k, it in enumerate(insts):
+                out = it.out if world == 1 else stage[b][(k % GE) * T:((k % GE) + 1) * T]
+                row.append((it.enc._h, vp(out.data_ptr()), vp(it.x.data_ptr()), vp(lens_np.ctypes.data), vp(0), ctypes.c_int(BATCH),
+                            vp(it.scratch.data_ptr()), ctypes.c_size_t(it.scratch.numel() * 2),
+                            vp(streams[k % ns].cuda_stream)))
+            calls.append(row)
 
         def step(i):
             k = i % len(insts)
@@ -480,7 +484,7 @@ def main():
                 group, slot = divmod(i, GE)
                 if group >= 3:
                     st.wait_event(ev_free[group % 3])   # the collective of group - 3 has read this buffer
-            rc = run_batch_c(*calls[k])
+            rc = run_batch_c(*calls[group % 3 if world > 1 else 0][k])
             if rc:
                 raise et.EtError(rc, et.lib().et_last_error().decode())
             if world > 1:
@@ -494,7 +498,8 @@ def main():
 
     def measure(insts, steps, warmup, ns=None):
         step = layer_step(insts, NS if ns is None else ns)
-        timed(step, 3 * len(insts), join, fork)   # direct run, graph capture and first replay of every instance
+        # direct run, graph capture and first replay of every instance (on every staging buffer it writes to)
+        timed(step, 3 * len(insts) * (3 if world > 1 else 1), join, fork)
         timed(step, warmup, join, fork)
         if world > 1:
             dist.barrier()
