@@ -71,14 +71,6 @@ extern "C" int et_debug_set_gemm_profile_buffer(void* dev_buf) {
     return ET_OK;
 }
 
-// Tuning experiments: force the tile GEMM's block-rows per CTA and ring depths for weights created afterwards
-// (0 = automatic).
-namespace et { void tile_gemm_set_tuning(int nb, int x_stages, int b_stages, int epi_bufs); }
-extern "C" int et_debug_set_gemm_tuning(int nb, int x_stages, int b_stages, int epi_bufs) {
-    et::tile_gemm_set_tuning(nb, x_stages, b_stages, epi_bufs);
-    return ET_OK;
-}
-
 namespace et { void attention_tc_set_profile_buffer(long long* dev_buf); }
 extern "C" int et_debug_set_attention_profile_buffer(void* dev_buf) {
     et::attention_tc_set_profile_buffer(static_cast<long long*>(dev_buf));

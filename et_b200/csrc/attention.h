@@ -18,7 +18,10 @@ int attention_launch(half* Z, const half* Q, const half* K, const half* V, const
 int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, int q_pitch, int v_pitch,
                         const half* mask, int mask_ld, const int* cu_seqlens, const int* valid_lens, int batch,
                         int uniform_len, int total_tokens, int max_len, int d_model, int nhead, cudaStream_t st);
+// Reads and clears the current device's error word of the tcgen05 kernel's bounded waits (synchronises).
 int attention_tc_error(int* code);
+// One-time per-device set-up of that error word (no allocation); safe to call repeatedly.
+int attention_prepare_device();
 int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, int d_model, int nhead,
                      cudaStream_t st);
 

@@ -18,6 +18,7 @@
 // shared memory and 256 TMEM columns and two CTAs share an SM: one CTA's softmax runs under the other's
 // UMMAs and loads. Every mbarrier wait is bounded; a wait that gives up
 // sets the error word and the CTA leaves through the common exit, freeing its tensor memory.
+#include <mutex>
 #include "attention.h"
 #include "common.h"
 #include "ptx.cuh"
@@ -514,10 +515,38 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
 
 long long* g_attn_prof = nullptr;
 
-int* g_tc_err = nullptr;   // device error word shared by all launches of this process, one per device would be
-int g_tc_err_dev = -1;     // better; the kernels only ever write non-zero on a timed-out wait
+// Error word of the kernel's bounded waits: a device variable of the library image (one copy per device that
+// loads the library, zero at load), so that no launch ever allocates. The kernel writes it only when a wait
+// gives up. In host code the symbol is a handle, not an address: the address is looked up once per device.
+__device__ int g_attn_err_word;
+constexpr int kMaxDevices = 64;
+std::mutex g_err_mu;
+int* g_err_ptr[kMaxDevices] = {nullptr};
+
+int attn_err_address(int** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_status(e, "attention: cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices) return fail(ET_ERR_UNSUPPORTED, "attention: device ordinal above 63");
+    std::lock_guard<std::mutex> lk(g_err_mu);
+    if (!g_err_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_attn_err_word);
+        if (e != cudaSuccess) return cuda_status(e, "attention: cudaGetSymbolAddress");
+        g_err_ptr[dev] = static_cast<int*>(p);
+    }
+    *out = g_err_ptr[dev];
+    return ET_OK;
+}
 
 }  // namespace
+
+// Looks up the error word's address on the current device (encoder constructors call this so that the first
+// launch, possibly inside a caller's stream capture, has nothing left to set up).
+int attention_prepare_device() {
+    int* p = nullptr;
+    return attn_err_address(&p);
+}
 
 // Fast path. Returns ET_ERR_UNSUPPORTED (without touching anything) when the case is outside its range, so the
 // caller can use the general kernel instead.
@@ -529,12 +558,10 @@ int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, in
     if ((q_pitch & 7) || (v_pitch & 7) || (d_model & 7) || !aligned16(Q) || !aligned16(K) || !aligned16(V) || !aligned16(Z))
         return ET_ERR_UNSUPPORTED;
     if (batch <= 0 || total_tokens <= 0) return ET_OK;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (!g_tc_err || g_tc_err_dev != dev) {
-        if (cudaMalloc(&g_tc_err, sizeof(int)) != cudaSuccess) return fail(ET_ERR_CUDA, "attention: cudaMalloc failed");
-        cudaMemset(g_tc_err, 0, sizeof(int));
-        g_tc_err_dev = dev;
+    int* err_word = nullptr;
+    {
+        const int rc = attn_err_address(&err_word);
+        if (rc) return rc;
     }
     CUtensorMap tq, tk, tv;
     const uint64_t rows = (uint64_t)total_tokens;
@@ -547,15 +574,14 @@ int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, in
     p.Z = Z; p.mask = mask; p.cu_seqlens = cu_seqlens; p.valid_lens = valid_lens;
     p.z_pitch = d_model; p.mask_ld = mask_ld; p.batch = batch; p.uniform_len = uniform_len;
     p.scale_log2 = kLog2e / sqrtf((float)kHD);
-    p.err = g_tc_err;
+    p.err = err_word;
     p.prof = g_attn_prof;
     const size_t smem = (size_t)kTile * 5 + sizeof(TcShared) + 1024;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
-        if (e != cudaSuccess) return cuda_status(e, "attention: shared memory opt-in");
-        attr_done = true;
-    }
+    static PerDeviceOnce once;
+    const cudaError_t attr_err = once.run([] {
+        return cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    });
+    if (attr_err != cudaSuccess) return cuda_status(attr_err, "attention: shared memory opt-in");
     const int nblk = cu_seqlens ? (total_tokens + kBQ - 1) / kBQ + batch : batch * ((uniform_len + kBQ - 1) / kBQ);
     return cuda_status(launch_pdl(attention_tc_kernel, dim3(nblk, nhead), dim3(kThreads), smem, st, tq, tk, tv, p),
                        "attention (tcgen05) launch");
@@ -563,13 +589,19 @@ int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, in
 
 void attention_tc_set_profile_buffer(long long* dev_buf) { g_attn_prof = dev_buf; }
 
-// Reads and clears the error word of the tcgen05 attention kernel (synchronises). 0 = no wait gave up.
+// Reads and clears the current device's error word of the tcgen05 attention kernel (synchronises).
+// 0 = no wait gave up since the last read.
 int attention_tc_error(int* code) {
     *code = 0;
-    if (!g_tc_err) return ET_OK;
-    cudaError_t e = cudaMemcpy(code, g_tc_err, sizeof(int), cudaMemcpyDeviceToHost);
+    int* word = nullptr;
+    int rc = attn_err_address(&word);
+    if (rc) return rc;
+    cudaError_t e = cudaMemcpy(code, word, sizeof(int), cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return cuda_status(e, "attention error read");
-    if (*code) cudaMemset(g_tc_err, 0, sizeof(int));
+    if (*code) {
+        e = cudaMemset(word, 0, sizeof(int));
+        if (e != cudaSuccess) return cuda_status(e, "attention error clear");
+    }
     return ET_OK;
 }
 

@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <mutex>
 #include "../../include/et_b200.h"
 
 namespace et {
@@ -30,6 +31,25 @@ inline int sm_count() {
     }();
     return n;
 }
+
+// Runs `f` once per device (function attributes such as the shared-memory opt-in belong to a device's context,
+// not to the process) and returns its result on every later call from that device.
+struct PerDeviceOnce {
+    std::mutex mu;
+    bool done[64] = {};
+    cudaError_t err[64] = {};
+    template <typename F>
+    cudaError_t run(F&& f) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+        std::lock_guard<std::mutex> lk(mu);
+        if (!done[dev]) {
+            err[dev] = f();
+            done[dev] = true;
+        }
+        return err[dev];
+    }
+};
 
 // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is still
 // running; it must execute pdl_wait() before it touches anything the predecessor writes or reads.

@@ -115,9 +115,7 @@ int row_spmm_raw(half* out, const half* in, const half* weight, const half* bias
             tw = it->second;
         }
     }
-    int rc = tile_weight_set_bias_device(tw, bias, st);
-    if (rc) return rc;
-    return tile_linear_run(tw, out, in, M, 0, st);
+    return tile_linear_run(tw, out, in, M, 0, st, bias);
 }
 
 void row_spmm_cache_clear() {
@@ -182,9 +180,13 @@ struct Encoder {
     std::vector<Replay> replays;
     bool use_graphs = true;
     StreamBridge bridge;
-    ~Encoder() {
+    void drop_replays() {
         for (auto& r : replays)
             if (r.exec) cudaGraphExecDestroy(r.exec);
+        replays.clear();
+    }
+    ~Encoder() {
+        drop_replays();
         for (auto* t : lin) tile_weight_free(t);
         tile_weight_free(qkv);
         delete rq; delete rk; delete rv;
@@ -193,6 +195,22 @@ struct Encoder {
         cudaFree(d_lens);
     }
 };
+
+// The device array of sequence offsets and key counts grows geometrically. A recorded graph holds the array's
+// address as a kernel argument, so every graph recorded with the old array is dropped before it is freed
+// (`drop` does that); the caller re-records on its next calls.
+template <typename Drop>
+static int grow_lens(int** d_lens, int* cap, int need, Drop&& drop) {
+    if (*cap >= need) return ET_OK;
+    drop();
+    int ncap = std::max(need, std::max(64, 2 * *cap));
+    int* fresh = nullptr;
+    if (cudaMalloc(&fresh, sizeof(int) * (size_t)ncap) != cudaSuccess) return fail(ET_ERR_CUDA, "lengths: cudaMalloc failed");
+    cudaFree(*d_lens);   // synchronises with work still reading the old array
+    *d_lens = fresh;
+    *cap = ncap;
+    return ET_OK;
+}
 
 static int upload_half(half** dst, const half* src_host, size_t n) {
     if (cudaMalloc(dst, n * sizeof(half)) != cudaSuccess) return fail(ET_ERR_CUDA, "encoder: cudaMalloc failed");
@@ -203,6 +221,11 @@ static int encoder_common(Encoder* e, int d_model, int seq_len, int nheads, half
                           const half* g1, const half* b1, const half* g2, const half* b2, const half* mask) {
     if (d_model <= 0 || seq_len <= 0 || nheads <= 0 || d_model % nheads) return fail(ET_ERR_INVALID, "encoder: bad dimensions");
     if (!g1 || !b1 || !g2 || !b2) return fail(ET_ERR_INVALID, "encoder: null LayerNorm parameter");
+    {
+        // nothing is left to set up when the first attention launch comes (it may sit inside a caller's capture)
+        const int rc = attention_prepare_device();
+        if (rc) return rc;
+    }
     e->d_model = d_model; e->seq_len = seq_len; e->nheads = nheads; e->buffer = buffer;
     const half* src[4] = {g1, b1, g2, b2};
     for (int i = 0; i < 4; ++i) {
@@ -577,14 +600,9 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
     const int* cu = nullptr;
     const int* vl = nullptr;
     if (!uniform || valid_lens_host) {
-        if (e->lens_cap < 2 * batch + 1) {
-            cudaFree(e->d_lens);
-            e->d_lens = nullptr;
-            if (cudaMalloc(&e->d_lens, sizeof(int) * (2 * batch + 1)) != cudaSuccess)
-                return et::fail(ET_ERR_CUDA, "et_encoder_run_batch: cudaMalloc failed");
-            e->lens_cap = 2 * batch + 1;
-        }
-        int rc = et::cuda_status(cudaMemcpyAsync(e->d_lens, meta.data(), sizeof(int) * (2 * batch + 1),
+        int rc = et::grow_lens(&e->d_lens, &e->lens_cap, 2 * batch + 1, [e] { e->drop_replays(); });
+        if (rc) return rc;
+        rc = et::cuda_status(cudaMemcpyAsync(e->d_lens, meta.data(), sizeof(int) * (2 * batch + 1),
                                                  cudaMemcpyHostToDevice, st), "et_encoder_run_batch: lengths upload");
         if (rc) return rc;
         if (!uniform) cu = e->d_lens;
@@ -597,7 +615,8 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
         return et::encoder_forward(e, static_cast<half*>(out), static_cast<const half*>(in),
                                    static_cast<half*>(scratch), T, cu, vl, batch, uniform ? seq_lens_host[0] : 0, st, max_len);
     std::vector<int64_t> key = {(int64_t)(intptr_t)out, (int64_t)(intptr_t)in, (int64_t)(intptr_t)scratch,
-                                (int64_t)batch, (int64_t)(valid_lens_host != nullptr), (int64_t)e->materialize_scores};
+                                (int64_t)batch, (int64_t)(valid_lens_host != nullptr), (int64_t)e->materialize_scores,
+                                (int64_t)(intptr_t)e->d_lens};
     for (int v : meta) key.push_back(v);
     Encoder::Replay* slot = nullptr;
     for (auto& r : e->replays)
@@ -643,6 +662,50 @@ int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* 
     return et::cuda_status(cudaGraphLaunch(slot->exec, st), "et_encoder_run_batch: graph launch");
 }
 
+// Reads and clears the error words of every kernel the layer launches: the tile GEMMs' (one per owned weight) and
+// the current device's attention word. Synchronises.
+static int encoder_check(Encoder* e, int* code) {
+    std::vector<et::TileWeight*> ws(e->lin, e->lin + 6);
+    ws.push_back(e->qkv);
+    for (RowWeight* r : {e->rq, e->rk, e->rv})
+        if (r) ws.push_back(r->tw);
+    for (et::TileWeight* w : ws) {
+        if (!w) continue;
+        int c = 0;
+        const int rc = et::tile_weight_error(w, &c);
+        if (rc) return rc;
+        if (c && !*code) *code = c;
+    }
+    int c = 0;
+    const int rc = et::attention_tc_error(&c);
+    if (rc) return rc;
+    if (c && !*code) *code = c;
+    return ET_OK;
+}
+
+int et_encoder_check(et_encoder* enc, int* code) {
+    ET_REQUIRE(enc && enc->e && code, "et_encoder_check: null pointer");
+    *code = 0;
+    const int rc = encoder_check(enc->e, code);
+    if (rc) return rc;
+    if (*code) {
+        et::set_error("encoder layer: device wait %d gave up", *code);
+        return ET_ERR_DEVICE_TIMEOUT;
+    }
+    return ET_OK;
+}
+
+int et_attention_check(int* code) {
+    ET_REQUIRE(code, "et_attention_check: null pointer");
+    const int rc = et::attention_tc_error(code);
+    if (rc) return rc;
+    if (*code) {
+        et::set_error("attention: device wait %d gave up", *code);
+        return ET_ERR_DEVICE_TIMEOUT;
+    }
+    return ET_OK;
+}
+
 int et_encoder_set_graph_replay(et_encoder* enc, int on) {
     ET_REQUIRE(enc && enc->e, "et_encoder_set_graph_replay: null encoder");
     enc->e->use_graphs = on != 0;
@@ -678,6 +741,20 @@ int et_model_destroy(et_model* model) {
 }
 
 int et_model_num_layers(const et_model* model) { return model && model->m ? (int)model->m->layers.size() : 0; }
+
+int et_model_check(et_model* model, int* code) {
+    ET_REQUIRE(model && model->m && code, "et_model_check: null pointer");
+    *code = 0;
+    for (Encoder* e : model->m->layers) {
+        const int rc = encoder_check(e, code);
+        if (rc) return rc;
+    }
+    if (*code) {
+        et::set_error("layer stack: device wait %d gave up", *code);
+        return ET_ERR_DEVICE_TIMEOUT;
+    }
+    return ET_OK;
+}
 
 int et_model_set_graph_replay(et_model* model, int on) {
     ET_REQUIRE(model && model->m, "et_model_set_graph_replay: null model");
@@ -747,14 +824,9 @@ int et_model_run_batch(et_model* model, void* out, const void* in, const int* se
     const int* cu = nullptr;
     const int* vl = nullptr;
     if (!uniform || valid_lens_host) {
-        if (m->lens_cap < 2 * batch + 1) {
-            cudaFree(m->d_lens);
-            m->d_lens = nullptr;
-            if (cudaMalloc(&m->d_lens, sizeof(int) * (2 * batch + 1)) != cudaSuccess)
-                return et::fail(ET_ERR_CUDA, "et_model_run_batch: cudaMalloc failed");
-            m->lens_cap = 2 * batch + 1;
-        }
-        int rc = et::cuda_status(cudaMemcpyAsync(m->d_lens, meta.data(), sizeof(int) * (2 * batch + 1),
+        int rc = et::grow_lens(&m->d_lens, &m->lens_cap, 2 * batch + 1, [m] { m->drop_replays(); });
+        if (rc) return rc;
+        rc = et::cuda_status(cudaMemcpyAsync(m->d_lens, meta.data(), sizeof(int) * (2 * batch + 1),
                                                  cudaMemcpyHostToDevice, st), "et_model_run_batch: lengths upload");
         if (rc) return rc;
         if (!uniform) cu = m->d_lens;
@@ -766,7 +838,7 @@ int et_model_run_batch(et_model* model, void* out, const void* in, const int* se
     if (!m->use_graphs || capturing) return et::model_forward(m, o, x, T, cu, vl, batch, ul, st, max_len);
     // First call with given buffers and lengths runs directly, the second is captured, later ones replay.
     std::vector<int64_t> key = {(int64_t)(intptr_t)out, (int64_t)(intptr_t)in, (int64_t)batch,
-                                (int64_t)(valid_lens_host != nullptr)};
+                                (int64_t)(valid_lens_host != nullptr), (int64_t)(intptr_t)m->d_lens};
     for (Encoder* e : m->layers) key.push_back((int64_t)e->materialize_scores);
     for (int v : meta) key.push_back(v);
     et::Model::Replay* slot = nullptr;

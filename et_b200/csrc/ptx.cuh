@@ -28,11 +28,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                  "r"(bytes)
                  : "memory");
 }
-// Adds to the pending transaction count without arriving.
-__device__ __forceinline__ void mbar_expect_tx_only(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-                 : "memory");
-}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -55,36 +50,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
-// The same for a wait that is expected to last: the thread asks to be suspended for up to `hint_ns` per try, so
-// that its polling does not take issue slots from the warps it is waiting for.
-#ifndef ET_WAIT_MODE
-#define ET_WAIT_MODE 1
-#endif
-__device__ __forceinline__ bool mbar_wait_idle(uint64_t* bar, uint32_t parity) {
-#if ET_WAIT_MODE == 1
-    for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n.reg .pred P;\n"
-            "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n"
-            "selp.u32 %0, 1, 0, P;\n}"
-            : "=r"(ok)
-            : "r"(smem_u32(bar)), "r"(parity), "r"(4000u)
-            : "memory");
-        if (ok) return true;
-    }
-    return false;
-#elif ET_WAIT_MODE == 2
-    for (uint32_t i = 0; i < kMbarSpinLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(40);
-    }
-    return false;
-#else
-    return mbar_wait(bar, parity);
-#endif
-}
-
 // ------------------------------------------------------------------ TMA
 __device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y,
                                             uint64_t* bar) {
@@ -110,9 +75,6 @@ __device__ __forceinline__ void tma_store_2d(const void* tmap, const void* src, 
 __device__ __forceinline__ void tma_store_commit() {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-__device__ __forceinline__ void tma_store_wait_all() {
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-}
 __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
@@ -124,9 +86,6 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
             "r"(smem_u32(dst)),
         "l"(src), "r"(bytes), "r"(smem_u32(bar))
         : "memory");
-}
-__device__ __forceinline__ void prefetch_tmap(const void* tmap) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
 // ------------------------------------------------------------------ tcgen05

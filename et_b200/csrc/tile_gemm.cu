@@ -71,13 +71,6 @@ struct GemmParams {
     long long* prof;         // optional per-role clock64 stamps of CTA (0,0) (ET_GEMM_PROFILE builds only)
 };
 
-// Timing experiments (never in the shipped library): -DET_GEMM_EXPERIMENT=<mask> removes one stage's work
-// while keeping every barrier hop, to see what a chunk's time is made of. 1: no weight copy, 2: no UMMAs,
-// 4: no tcgen05.cp, 8: no activation TMA.
-#ifndef ET_GEMM_EXPERIMENT
-#define ET_GEMM_EXPERIMENT 0
-#endif
-
 #ifdef ET_GEMM_PROFILE
 #define ET_STAMP(slot) do { if (p.prof && blockIdx.x == 0 && blockIdx.y == 0) p.prof[(slot)] = clock64(); } while (0)
 #else
@@ -322,12 +315,10 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 if (lane == 0) {
                     const uint32_t xa = smem_u32(xbase + (size_t)bs * slot_bytes);
                     const uint32_t ta = tmem + a_col0 + a * kSlotCols;
-                    if (!(ET_GEMM_EXPERIMENT & 4)) {
 #pragma unroll
-                        for (int sl = 0; sl < kSlices; ++sl)
-                            tc_cp_128x256b(ta + sl * 8,
-                                           make_smem_desc(xa + (sl >> 2) * kPanelBytes + (sl & 3) * 32, 16, 1024, 2));
-                    }
+                    for (int sl = 0; sl < kSlices; ++sl)
+                        tc_cp_128x256b(ta + sl * 8,
+                                       make_smem_desc(xa + (sl >> 2) * kPanelBytes + (sl & 3) * 32, 16, 1024, 2));
                     umma_commit(&sh->a_ready[a]);
                     if (it < 64) ET_STAMP(300 + it);
                 }
@@ -396,7 +387,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll 4
                     for (int i = 0; i < ne; ++i) {
                         const uint4 e = ent[i];
-                        if (!(ET_GEMM_EXPERIMENT & 2) && elect_one())
+                        if (elect_one())
                             umma_f16_ts(tmem + e.z, abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
                     }
                     if (elect_one()) umma_commit(&sh->done[bs]);
@@ -502,16 +493,14 @@ struct TileWeight {
 // stage. A stage goes round in ~4000 clocks (TMA, tcgen05.cp, UMMAs, and the polls between them), a
 // tensor-memory slot in ~2000.
 struct RingShape { int stages, a_slots, epi_bufs; double period; };
-// Tuning experiments: {block-rows per CTA, stages, unused, staging buffers}, 0 = automatic.
-static int g_tune[4] = {0, 0, 0, 0};
 static RingShape ring_shape(int nb, int stage_b_bytes) {
     const int tmem_slots = std::min(kMaxRing, (512 - nb * 16) / kSlotCols);
     const int slot = kXStageBytes + stage_b_bytes;
     const int avail1 = kSmemMax - 1024 - (int)sizeof(Shared) - kIssuers * kUnitBytes;
-    const int cap = g_tune[1] > 0 ? std::min(g_tune[1], kMaxRing) : 4;
+    const int cap = 4;
     RingShape r;
     r.stages = std::min(cap, avail1 / slot);
-    r.epi_bufs = (avail1 - r.stages * slot >= kIssuers * kUnitBytes && g_tune[3] != 1) ? 2 : 1;
+    r.epi_bufs = (avail1 - r.stages * slot >= kIssuers * kUnitBytes) ? 2 : 1;
     r.a_slots = std::min(r.stages, tmem_slots);
     r.period = r.stages >= 1 && r.a_slots >= 1 ? std::max(4000.0 / r.stages, 2000.0 / r.a_slots) : 1e30;
     return r;
@@ -568,10 +557,9 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
 
     auto* w = new TileWeight();
     w->K = K; w->N = N; w->ntile = ntile; w->size_hint = size_hint;
-    w->tiles_per_cta = g_tune[2] > 0 ? g_tune[2] : (g_goal == 1 ? kThroughputTilesPerCta : 1);
+    w->tiles_per_cta = g_goal == 1 ? kThroughputTilesPerCta : 1;
     const double density = (double)ntile / std::max(1.0, (double)NBR * (K / 16));
     w->nb = choose_nb(NBR, (K + kKC - 1) / kKC, size_hint, density);
-    if (nb_override <= 0 && g_tune[0] > 0) nb_override = g_tune[0];
     if (nb_override > 0) {
         const int nbo = std::min(nb_override, kMaxNB);
         w->nb = NBR <= nbo ? NBR : std::max(4, nbo / 4 * 4);
@@ -681,17 +669,10 @@ void tile_weight_free(TileWeight* w) {
     delete w;
 }
 
-int tile_weight_set_bias_device(TileWeight* w, const half* bias_dev, cudaStream_t st) {
-    return cuda_status(cudaMemcpyAsync(w->d_bias, bias_dev, (size_t)w->N * sizeof(half), cudaMemcpyDeviceToDevice, st), "bias copy");
-}
-
-void tile_gemm_set_tuning(int nb, int x_stages, int b_stages, int epi_bufs) {
-    g_tune[0] = nb; g_tune[1] = x_stages; g_tune[2] = b_stages; g_tune[3] = epi_bufs;
-}
 static long long* g_prof = nullptr;
 void tile_gemm_set_profile_buffer(long long* dev_buf) { g_prof = dev_buf; }
 
-int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st) {
+int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st, const half* bias_dev) {
     if (!w || !Y || !X) return fail(ET_ERR_INVALID, "tile linear: null pointer");
     if (T < 0) return fail(ET_ERR_INVALID, "tile linear: negative token count");
     if (T == 0) return ET_OK;
@@ -700,16 +681,16 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     if (!make_tmap_panels_f16(&tm, X, (uint64_t)T, (uint64_t)w->K, (uint64_t)w->K, kSlab, kKC / kPanel) ||
         !make_tmap_2d_f16(&tmy, Y, (uint64_t)T, (uint64_t)w->N, (uint64_t)w->N, 32, kUnitCols, 64))
         return fail(ET_ERR_CUDA, "tile linear: cuTensorMapEncodeTiled failed");
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(tile_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
-        if (attr_err == cudaSuccess)
-            attr_err = cudaFuncSetAttribute(tile_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+    static PerDeviceOnce once;
+    const cudaError_t attr_err = once.run([] {
+        cudaError_t e = cudaFuncSetAttribute(tile_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(tile_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        return e;
     });
     if (attr_err != cudaSuccess) return cuda_status(attr_err, "tile linear: shared memory opt-in");
     GemmParams p;
-    p.dir = w->d_dir; p.stream = w->d_stream; p.Y = Y; p.bias = w->d_bias;
+    p.dir = w->d_dir; p.stream = w->d_stream; p.Y = Y; p.bias = bias_dev ? bias_dev : w->d_bias;
     p.T = T; p.N = w->N; p.k_chunks = w->k_chunks; p.nb = w->nb;
     p.n_chunks = w->n_chunks;
     p.n_tiles = ((T + kSlab - 1) / kSlab) * w->n_chunks;
@@ -777,9 +758,8 @@ int tile_spmm_raw(half* Y, const half* X, const int* row_ptr, const int* row_off
             w = it->second;
         }
     }
-    int rc = tile_weight_set_bias_device(w, bias, st);
-    if (rc) return rc;
-    return tile_linear_run(w, Y, X, M, gelu, st);
+    // the caller's bias is a kernel argument: nothing of the call is kept in the cached weight
+    return tile_linear_run(w, Y, X, M, gelu, st, bias);
 }
 
 void tile_spmm_cache_clear() {

@@ -15,8 +15,9 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
 int tile_weight_concat(TileWeight** out, const TileWeight* const* parts, int count, int size_hint);
 int tile_weight_out_feat(const TileWeight* w);
 void tile_weight_free(TileWeight* w);
-int tile_weight_set_bias_device(TileWeight* w, const half* bias_dev, cudaStream_t st);
-int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st);
+// bias_dev != null replaces the weight's own bias for this launch (device pointer, N halfs).
+int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st,
+                    const half* bias_dev = nullptr);
 // Reads and clears the device error word (0 = no bounded wait gave up). Synchronises.
 int tile_weight_error(const TileWeight* w, int* code);
 void tile_weight_info(const TileWeight* w, int* info6);

@@ -14,7 +14,7 @@ __all__ = [
     "RowWeight", "attention_otf", "attention_prune", "qk_scores", "attention_sharedqk", "attention_batch", "attention_static_scores",
     "gen_sparse_tile_mat", "gen_sparse_row_mat", "build_head_ptr", "Encoder", "encoder_buffer_size",
     "encoder_batch_buffer_size", "KIND_TILE", "KIND_PRUNE", "KIND_LENGTH", "KIND_PRUNE_QKV",
-    "Model", "prune_dense_to_tiles", "select_rows_magnitude", "compact_rows", "set_tuning_goal",
+    "Model", "attention_check", "prune_dense_to_tiles", "select_rows_magnitude", "compact_rows", "set_tuning_goal",
 ]
 
 _i = ctypes.c_int
@@ -168,6 +168,13 @@ def attention_static_scores(out, Q, K, V, mask, seq_len, d_model, nhead, stream=
     return out
 
 
+def attention_check():
+    """Raises EtError (ET_ERR_DEVICE_TIMEOUT) if a bounded wait of the tensor-core attention kernel gave up on the
+    current device since the last check; synchronises."""
+    code = _i(0)
+    check(lib().et_attention_check(ctypes.byref(code)))
+
+
 def attention_batch(out, Q, K, V, d_model, nhead, cu_seqlens=None, valid_lens=None, batch=1, uniform_len=0,
                     max_seq_len=0, total_tokens=None, mask=None, mask_ld=0, qk_pitch=None, v_pitch=None, qk_head_ptr=None,
                     v_col_id=None, v_head_ptr=None, stream=None):
@@ -264,6 +271,11 @@ class Encoder:
                                          stream_ptr(stream)))
         return out
 
+    def check(self):
+        """Raises EtError (ET_ERR_DEVICE_TIMEOUT) if a device-side wait of one of the layer's kernels gave up."""
+        code = _i(0)
+        check(lib().et_encoder_check(self._h, ctypes.byref(code)))
+
     def set_graph_replay(self, on):
         check(lib().et_encoder_set_graph_replay(self._h, _i(1 if on else 0)))
 
@@ -305,6 +317,11 @@ class Model:
         check(lib().et_model_run_batch(self._h, ptr(out), ptr(x), ptr(seq_lens), ptr(valid), _i(len(seq_lens)),
                                        stream_ptr(stream)))
         return out
+
+    def check(self):
+        """Raises EtError (ET_ERR_DEVICE_TIMEOUT) if a device-side wait of one of the stack's kernels gave up."""
+        code = _i(0)
+        check(lib().et_model_check(self._h, ctypes.byref(code)))
 
     def set_graph_replay(self, on):
         check(lib().et_model_set_graph_replay(self._h, _i(1 if on else 0)))

@@ -69,8 +69,11 @@ int et_set_tuning_goal(int goal);
 /* info[6] = {block_rows_per_cta, n_chunks, k_chunks, stages, stage_bytes, packed_bytes}. */
 int et_tile_weight_info(const et_tile_weight* w, int* info);
 /* Same contraction from DEVICE-resident tile arrays, K = in_feat explicit. The packed form of a
- * weight is built on its first use (device-to-host copy, synchronous) and cached by array address;
- * call et_tile_spmm_cache_clear() after changing a weight in place. Replaces
+ * weight is built on its first use (device-to-host copy, synchronous: not inside a stream capture) and cached
+ * by the three array addresses, N and K; the bias is read from the caller's pointer at every call. Call
+ * et_tile_spmm_cache_clear() after changing a weight in place AND after freeing one: a new weight of the same
+ * shape that the allocator places at the same addresses would otherwise be served the old packed copy
+ * (objects that own their weight, et_tile_weight_create / Linear_tile, have no such hazard). Replaces
  * tile_spmm_add_bias_kernelLauncher / tile_spmm_add_bias_gelu_kernelLauncher
  * (kernels/kernels.h:13-20, kernels/linear.cu:152-167), whose missing K is the row pitch of X. */
 int et_tile_spmm_bias(void* Y, const void* X, const int* W_row_ptr, const int* W_row_offset,
@@ -92,7 +95,8 @@ int et_row_weight_destroy(et_row_weight* w);
 int et_row_linear(const et_row_weight* w, void* out, const void* in, int tokens, void* stream);
 /* Same contraction from a DEVICE-resident dense compact weight [N x K], N and K multiples of 16 (the
  * reference pads N to 16): out[M x N] = in[M x K] . weight^T + bias. Packed on first use and cached by
- * weight address (et_tile_spmm_cache_clear drops the cache). Replaces row_spmm_add_bias_kernelLauncher
+ * weight address, N and K, with the same address-reuse hazard as et_tile_spmm_bias (et_tile_spmm_cache_clear
+ * drops the cache); the bias is read from the caller's pointer at every call. Replaces row_spmm_add_bias_kernelLauncher
  * (kernels/kernels.h:7-11, kernels/linear.cu:18-34) without its cuBLAS handle and algorithm. */
 int et_row_spmm_bias(void* out, const void* in, const void* weight, const void* bias, int M, int N, int K,
                      void* stream);
@@ -130,6 +134,12 @@ int et_attention_sharedqk(void* out, const void* QK, const void* V, const void* 
  * on the GPU race. Nothing needs clearing between calls. */
 int et_attention_static_scores(void* out, const void* Q, const void* K, const void* V, const void* mask,
                                int seq_len, int d_model, int nhead, void* stream);
+/* Reads and clears the current device's error word of the tensor-core attention kernel (synchronises):
+ * ET_ERR_DEVICE_TIMEOUT and the code in *code (21: the issuing thread's wait, 22: the final accumulator wait)
+ * when a bounded wait inside the kernel gave up since the last check; the rows of that CTA are then not
+ * written. The word is one per device, shared by every launch on it. No counterpart in the reference, whose
+ * only error handling is cudaChk's exit(1) (encoder/utils.h:4-12). */
+int et_attention_check(int* code);
 /* Batched, variable-length form (no counterpart in the reference, which handles one sequence per call):
  * sequences are packed back to back; cu_seqlens (device, batch+1 ints) gives their token offsets, or NULL
  * for `batch` sequences of uniform_len tokens. valid_lens (device, may be NULL) excludes keys at or beyond
@@ -206,6 +216,11 @@ int et_encoder_run(et_encoder* enc, void* out, const void* in, void* stream);
  * scratch: device buffer of et_encoder_batch_buffer_size bytes. */
 int et_encoder_run_batch(et_encoder* enc, void* out, const void* in, const int* seq_lens_host,
                          const int* valid_lens_host, int batch, void* scratch, size_t scratch_bytes, void* stream);
+/* Reads and clears the error words of every kernel the layer launches (its tile GEMMs and the device's
+ * attention word, see et_attention_check); synchronises. ET_ERR_DEVICE_TIMEOUT with the first code found in
+ * *code when a bounded device-side wait gave up since the last check: the output of that run is then
+ * incomplete. The status a caller reads where the reference would have exited (encoder/utils.h:4-12). */
+int et_encoder_check(et_encoder* enc, int* code);
 /* et_encoder_run_batch replays a CUDA graph of the layer's launches from the third call on with the same
  * buffers and lengths (no counterpart in the reference, whose run() blocks the host three times per layer).
  * on = 0 turns that off (plain launches every call). It is skipped by itself while the caller's stream is
@@ -229,6 +244,8 @@ int et_model_reserve(et_model* model, int total_tokens, int batch, int max_len);
 int et_model_run_batch(et_model* model, void* out, const void* in, const int* seq_lens_host,
                        const int* valid_lens_host, int batch, void* stream);
 int et_model_set_graph_replay(et_model* model, int on);
+/* et_encoder_check over every layer of the stack (encoder/utils.h:4-12 is the reference's error path). */
+int et_model_check(et_model* model, int* code);
 
 #ifdef __cplusplus
 }

@@ -84,6 +84,61 @@ def test_encoder_tile_batch_config2(et, orc, sparsity):
     util.assert_close(host(out), want, what=f"config 2 sparsity={sparsity}")
 
 
+def test_encoder_tile_batch_config2_packed_for_throughput(et, orc):
+    """Config 2 with the weights packed under the throughput goal, several calls in a row so that the direct run,
+    the graph capture and the replays are all compared with the oracle."""
+    d, H, dff, B, S = 768, 12, 3072, 16, 128
+    lin, ln = make_layer(orc, d, dff, 0.75, seed=12)
+    et.set_tuning_goal("throughput")
+    try:
+        enc = build_encoder(et, et.KIND_TILE, lin, ln, d, S, H, B * S)
+    finally:
+        et.set_tuning_goal("latency")
+    X = util.activations(18, (B * S, d))
+    want = orc.encoder_layer(X, orc_lin(lin), ln, [S] * B, d, H)
+    scratch = torch.zeros(et.encoder_batch_buffer_size(et.KIND_TILE, d, B * S, B, S, H) // 2,
+                          dtype=torch.float16, device="cuda")
+    x = dev(X)
+    side = torch.cuda.Stream()
+    for call in range(4):
+        out = torch.full((B * S, d), float("nan"), dtype=torch.float16, device="cuda")
+        with torch.cuda.stream(side):
+            enc.run_batch(out, x, [S] * B, scratch)
+        torch.cuda.synchronize()
+        util.assert_close(host(out), want, what=f"config 2, throughput packing, call {call}")
+    enc.check()
+
+
+def test_run_batch_alternating_batch_sizes_keeps_replayed_graphs_valid(et, orc):
+    """Variable-length batches of 4, then 8, then the first 4 again, three or more calls each: the device array of
+    lengths grows in between, and the graphs recorded before that must not be replayed against the old array."""
+    d, H, dff = 768, 12, 3072
+    lin, ln = make_layer(orc, d, dff, 0.75, seed=13)
+    lens_a = [40, 128, 17, 96]
+    lens_b = [64, 33, 128, 90, 5, 77, 128, 100]
+    # a third shape that needs more than the first allocation's 64 entries
+    lens_c = [16 + (7 * i) % 48 for i in range(40)]
+    enc = build_encoder(et, et.KIND_LENGTH, lin, ln, d, 128, H, sum(lens_b))
+    stream = torch.cuda.Stream()
+    cases = {}
+    for name, lens in (("a", lens_a), ("b", lens_b), ("c", lens_c)):
+        T = sum(lens)
+        X = util.activations(30 + len(lens), (T, d))
+        cases[name] = (lens, dev(X), torch.zeros((T, d), dtype=torch.float16, device="cuda"),
+                       orc.encoder_layer(X, orc_lin(lin), ln, lens, d, H))
+    Tmax = max(sum(c[0]) for c in cases.values())
+    scratch = torch.zeros(et.encoder_batch_buffer_size(et.KIND_LENGTH, d, Tmax, 40, 128, H) // 2,
+                          dtype=torch.float16, device="cuda")
+    for name in ("a", "a", "a", "b", "b", "b", "a", "a", "c", "c", "c", "a", "b", "a"):
+        lens, x, out, want = cases[name]
+        out.fill_(float("nan"))
+        with torch.cuda.stream(stream):
+            enc.run_batch(out, x, lens, scratch)
+        torch.cuda.synchronize()
+        util.assert_close(host(out), want, what=f"alternating varlen batches, case {name}")
+    enc.check()
+
+
 def test_encoder_length_varlen_equals_padded_and_oracle(et, orc):
     """Config 4 mechanics at reduced size: variable lengths (not multiples of 16) vs the same batch padded to
     max length with key padding; both match the oracle on the valid tokens; materialised-score path too."""

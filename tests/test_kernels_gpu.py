@@ -143,6 +143,26 @@ def test_tile_linear_all_chunkings(et, orc, size_hint):
     util.assert_close(got, want, what=f"tile linear hint {size_hint} {w.info()}")
 
 
+@pytest.mark.parametrize("T,K,N,sparsity,gelu", [
+    (2048, 768, 2304, 0.75, False),   # the fused Q|K|V shape of the 16 x 128 tile layer
+    (2048, 768, 768, 0.75, False),
+    (2048, 768, 3072, 0.75, True),
+    (2048, 3072, 768, 0.75, False),
+    (2048, 768, 768, 0.5, False),
+    (4096, 1024, 4096, 0.8, True),    # BERT-large FFN1 slab count above one wave of two-tile CTAs
+    (300, 768, 3072, 0.9, True),      # ragged token count, under-filled grid, odd tile count per CTA
+])
+def test_tile_linear_packed_for_throughput(et, orc, T, K, N, sparsity, gelu):
+    """Weights packed under the throughput goal (larger chunks, two tiles per CTA): the configuration a caller
+    with several batches in flight uses. Same oracle, same tolerance."""
+    et.set_tuning_goal("throughput")
+    try:
+        got, want, w = _run_tile(et, orc, T, K, N, sparsity, seed=T + K + N + 1, gelu=gelu)
+    finally:
+        et.set_tuning_goal("latency")
+    util.assert_close(got, want, what=f"tile linear (throughput packing) T={T} K={K} N={N} s={sparsity} {w.info()}")
+
+
 def test_tile_linear_pruned_tiles_do_not_contribute(et, orc):
     """Mask exactness: output equals the dense product with the pruned tiles zeroed, and does not
     change when garbage is placed where the pruned tiles would be."""

@@ -58,6 +58,33 @@ def test_model_equals_layers_one_by_one_and_oracle(et, orc):
     assert torch.equal(xe, ref)
 
 
+def test_model_alternating_batch_sizes(et, orc):
+    """The stack's own array of lengths grows when a larger batch arrives; graphs recorded before that are
+    re-recorded, and every call matches a run without graph replay."""
+    d, H, dff, n_layers = 256, 4, 1024, 2
+    layers = [make_layer(orc, d, dff, 0.5, seed=60 + 7 * i) for i in range(n_layers)]
+    model = et.Model([build_encoder(et, et.KIND_TILE, lin, ln, d, 128, H, 512) for lin, ln in layers])
+    plain = et.Model([build_encoder(et, et.KIND_TILE, lin, ln, d, 128, H, 512) for lin, ln in layers])
+    plain.set_graph_replay(False)
+    cases = {"a": [50, 128, 17, 96], "b": [64, 33, 128, 90, 5, 77, 128, 100], "c": [8 + (5 * i) % 40 for i in range(70)]}
+    data = {}
+    for name, lens in cases.items():
+        x = dev(util.activations(70 + len(lens), (sum(lens), d)))
+        want = torch.zeros_like(x)
+        plain.run_batch(want, x, lens)
+        data[name] = (lens, x, torch.zeros_like(x), want)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    for name in ("a", "a", "a", "b", "b", "b", "a", "a", "c", "c", "c", "a", "b"):
+        lens, x, out, want = data[name]
+        out.fill_(float("nan"))
+        with torch.cuda.stream(stream):
+            model.run_batch(out, x, lens)
+        torch.cuda.synchronize()
+        assert torch.equal(out, want), f"case {name}"
+    model.check()
+
+
 def test_model_argument_checks(et, orc):
     d, H, dff = 128, 2, 256
     lin, ln = make_layer(orc, d, dff, 0.5, seed=40)

@@ -4,7 +4,7 @@ Some callers of this library have no way to allocate device memory when they run
 plan, a host process that owns the allocator). et_attention_static_scores serves them from a score buffer
 built into the library. This file checks it against et_attention_otf on two calls in a row, the second with
 other inputs and a shorter sequence so that whatever the first call left in the shared buffer cannot help.
-It is collected last so that a run stopping at the first failure has already executed every other test.
+Both are also compared with the fp32 CPU oracle. It is collected last so that a run stopping at the first failure has already executed every other test.
 """
 import ctypes
 
@@ -38,6 +38,10 @@ def test_static_score_attention_matches_on_the_fly_twice():
         # fp16-vs-oracle comparison of this suite
         util.assert_close(got.float().cpu().numpy(), want.float().cpu().numpy(),
                           what=f"static-score attention, call {call}")
+        from tests import oracle_lib
+        ref = oracle_lib.load().attention(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), [seq], d, H,
+                                          mask=mask.float().cpu().numpy())
+        util.assert_close(got.float().cpu().numpy(), ref, what=f"static-score attention vs the oracle, call {call}")
 
 
 def test_static_score_attention_rejects_oversize():
