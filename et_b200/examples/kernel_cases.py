@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """One kernel at a time on inputs larger than L2: prints the achieved rate from CUDA events.
 
-    python et_b200/examples/kernel_cases.py {gemm|attention|attention512|attention_mma|layernorm|softmax} [launches]
+    python et_b200/examples/kernel_cases.py {gemm|gemm_large|attention|attention512|attention_mma|layernorm|softmax} [launches]
 
 `attention_mma` is `attention` with the lengths given only on the device, which the tcgen05 kernel declines
 (it needs the longest length on the host), so the mma.sync kernel runs.
@@ -36,8 +36,9 @@ def timed(fn, n):
 def main():
     case = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     n = int(sys.argv[2]) if len(sys.argv) > 2 else 5
-    if case == "gemm":
-        T, K, N, sparsity = 16384, 768, 3072, 0.75
+    if case in ("gemm", "gemm_large"):
+        # gemm: the base model's FFN1 shape; gemm_large: BERT-large's (in 1024, out 4096, 80 % of the tiles pruned)
+        T, K, N, sparsity = (16384, 768, 3072, 0.75) if case == "gemm" else (16384, 1024, 4096, 0.8)
         rp, ro = et.gen_sparse_tile_mat(N, K, sparsity, 7, bernoulli=True)
         rng = np.random.default_rng(0)
         data = (rng.standard_normal((len(ro), 256), dtype=np.float32) * 0.02).astype(np.float16)

@@ -9,7 +9,7 @@
 // executables print nothing and check nothing), so this oracle cannot be pinned against
 // reference golden vectors. It is pinned instead against outputs of the reference's own
 // CUDA kernels run on a B200 (fixtures under tests/golden/, produced by
-// tests/golden/make_ref_fixtures.py) in the `ET_ORC_REF_COMPAT` mode that reproduces the
+// tests/golden/make_golden.py) in the `ET_ORC_REF_COMPAT` mode that reproduces the
 // reference's base-2 exponent and zero-initialised row max.
 //
 // Reference files restated here (paths inside the reference project):

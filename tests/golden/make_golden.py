@@ -97,8 +97,9 @@ def main():
     out["sharedqk"] = Z.cpu().numpy()
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_kernels.npz")
     np.savez_compressed(dst, **out)
-    if os.path.isdir(os.path.join(ROOT, "gpurun_out")):
-        np.savez_compressed(os.path.join(ROOT, "gpurun_out", "reference_kernels.npz"), **out)
+    extra = os.environ.get("ET_GOLDEN_COPY_DIR")   # optional second copy (e.g. a folder that is carried back from a remote run)
+    if extra and os.path.isdir(extra):
+        np.savez_compressed(os.path.join(extra, "reference_kernels.npz"), **out)
     print("wrote", dst, {k: v.shape for k, v in out.items()})
 
 

@@ -21,7 +21,7 @@ def _no_gpu():
 @pytest.mark.skipif(not _no_gpu(), reason="checks the behaviour without a GPU")
 def test_reference_arm_falls_back_to_the_cpu_oracle():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "3", "--warmup", "3",
-                        "--batch", "2", "--seq", "64"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+                        "--seq", "64"], capture_output=True, text=True, timeout=600, cwd=ROOT)
     assert r.returncode == 0, r.stderr[-2000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
     d = json.loads(line)
