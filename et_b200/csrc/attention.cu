@@ -375,7 +375,8 @@ __global__ void __launch_bounds__(128) qk_scores_kernel(half* __restrict__ S, co
 }  // namespace
 
 int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, int d_model, int nhead,
-                     cudaStream_t st) {
+                     cudaStream_t st, int pitch) {
+    if (pitch <= 0) pitch = d_model;
     if (!S || !Q || !K) return fail(ET_ERR_INVALID, "qk scores: null pointer");
     if (batch < 0 || L < 0 || nhead <= 0 || d_model <= 0 || d_model % nhead) return fail(ET_ERR_INVALID, "qk scores: bad dimensions");
     const int hd = d_model / nhead;
@@ -383,7 +384,7 @@ int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, in
     if (batch == 0 || L == 0) return ET_OK;
     if ((long)batch * nhead > 65535) return fail(ET_ERR_UNSUPPORTED, "qk scores: batch*nhead above 65535");
     dim3 grid((L + kBQ - 1) / kBQ, (L + kBK - 1) / kBK, batch * nhead);
-    return cuda_status(launch_pdl(qk_scores_kernel, grid, dim3(128), 0, st, S, Q, K, L, d_model, nhead, hd,
+    return cuda_status(launch_pdl(qk_scores_kernel, grid, dim3(128), 0, st, S, Q, K, L, pitch, nhead, hd,
                                   1.0f / sqrtf((float)hd)),
                        "qk scores launch");
 }

@@ -22,8 +22,9 @@ int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, in
 int attention_tc_error(int* code);
 // One-time per-device set-up of that error word (no allocation); safe to call repeatedly.
 int attention_prepare_device();
+// pitch: row pitch of Q and K in elements (0 = d_model).
 int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, int d_model, int nhead,
-                     cudaStream_t st);
+                     cudaStream_t st, int pitch = 0);
 
 // Same result as the on-the-fly form for one sequence, through scores held in a device array that is part
 // of the library image (no allocation). seq_len*seq_len*nhead is limited to 16*512*512.

@@ -165,6 +165,7 @@ struct Encoder {
     half* buffer = nullptr;  // caller-owned scratch for run(): buffer_num * seq_len * d_model halfs (+ scores)
     TileWeight* lin[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v o mlp1 mlp2
     TileWeight* qkv = nullptr;   // Q|K|V as one weight: one launch, one staging of the activations per CTA
+    int qkv_cols[3] = {0, 0, 0}; // output columns of the three parts inside the fused result
     RowWeight* rq = nullptr; RowWeight* rk = nullptr; RowWeight* rv = nullptr;
     half* d_ln[4] = {nullptr, nullptr, nullptr, nullptr};  // gamma1 beta1 gamma2 beta2
     half* d_mask = nullptr;                                // [seq_len x seq_len] additive, may be null
@@ -247,11 +248,14 @@ static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch,
     int q_pitch = e->d_model, v_pitch = e->d_model;
     const int *qk_hp = nullptr, *v_hp = nullptr, *v_id = nullptr;
     if (e->qkv) {
-        // fused: [T x 3 d_model] over the first three scratch buffers, Q | K | V side by side
+        // fused: one launch writes Q | K | V side by side, [T x (q + k + v columns)] over the first three scratch
+        // buffers (row-pruned parts are compact, so the three widths may differ)
         if ((rc = tile_linear_run(e->qkv, b0, in, T, 0, st))) return rc;
-        q_pitch = v_pitch = 3 * e->d_model;
-        b1 = b0 + e->d_model;
-        b2 = b0 + 2 * e->d_model;
+        q_pitch = v_pitch = e->qkv_cols[0] + e->qkv_cols[1] + e->qkv_cols[2];
+        b1 = b0 + e->qkv_cols[0];
+        b2 = b1 + e->qkv_cols[1];
+        if (e->kind == kPruneQKV) qk_hp = e->rq->d_head_ptr;
+        if (e->kind == kPrune || e->kind == kPruneQKV) { v_hp = e->rv->d_head_ptr; v_id = e->rv->d_row_id; }
     } else if (e->kind == kPruneQKV) {
         if ((rc = tile_linear_run(e->rq->tw, b0, in, T, 0, st))) return rc;
         if ((rc = tile_linear_run(e->rk->tw, b1, in, T, 0, st))) return rc;
@@ -270,7 +274,7 @@ static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch,
     const half* scores = nullptr;
     if (e->kind == kLength && e->materialize_scores && !cu_seqlens) {
         half* sbuf = scratch + 5 * td;
-        if ((rc = qk_scores_launch(sbuf, b0, b1, batch, uniform_len, e->d_model, e->nheads, st))) return rc;
+        if ((rc = qk_scores_launch(sbuf, b0, b1, batch, uniform_len, e->d_model, e->nheads, st, q_pitch))) return rc;
         scores = sbuf;
     }
     if ((rc = attention_launch(b3, b0, b1, b2, scores, q_pitch, v_pitch, qk_hp, v_id, v_hp, e->d_mask, e->seq_len,
@@ -478,6 +482,7 @@ int et_encoder_tile_create(et_encoder** out, int kind, int d_model, int seq_len,
         et::tile_weight_out_feat(e->lin[2]) == d_model) {
         const et::TileWeight* parts[3] = {e->lin[0], e->lin[1], e->lin[2]};
         if ((rc = et::tile_weight_concat(&e->qkv, parts, 3, 0))) return rc;
+        for (int i = 0; i < 3; ++i) e->qkv_cols[i] = d_model;
     }
     return finish_create(out, e);
 }
@@ -502,6 +507,14 @@ int et_encoder_prune_create(et_encoder** out, int d_model, int seq_len, int nhea
     if ((rc = take_tiles(e.get(), t01, 0, 2, d_model))) return rc;
     if ((rc = take_tiles(e.get(), t35, 3, 3, d_model))) return rc;
     e->rv = v->w; v->w = nullptr;
+    if (et::tile_weight_out_feat(e->lin[0]) == d_model && et::tile_weight_out_feat(e->lin[1]) == d_model &&
+        e->rv->in_feat == d_model) {
+        // Q | K | compact V in one launch
+        const et::TileWeight* parts[3] = {e->lin[0], e->lin[1], e->rv->tw};
+        if ((rc = et::tile_weight_concat(&e->qkv, parts, 3, 0))) return rc;
+        e->qkv_cols[0] = e->qkv_cols[1] = d_model;
+        e->qkv_cols[2] = e->rv->nrow;
+    }
     return finish_create(out, e);
 }
 
@@ -527,6 +540,13 @@ int et_encoder_prune_qkv_create(et_encoder** out, int d_model, int seq_len, int 
     e->rq = q->w; q->w = nullptr;
     e->rk = k->w; k->w = nullptr;
     e->rv = v->w; v->w = nullptr;
+    if (e->rq->in_feat == d_model && e->rk->in_feat == d_model && e->rv->in_feat == d_model &&
+        e->rq->nrow + e->rk->nrow + e->rv->nrow <= 3 * d_model) {
+        // compact Q | K | V in one launch
+        const et::TileWeight* parts[3] = {e->rq->tw, e->rk->tw, e->rv->tw};
+        if ((rc = et::tile_weight_concat(&e->qkv, parts, 3, 0))) return rc;
+        e->qkv_cols[0] = e->rq->nrow; e->qkv_cols[1] = e->rk->nrow; e->qkv_cols[2] = e->rv->nrow;
+    }
     return finish_create(out, e);
 }
 

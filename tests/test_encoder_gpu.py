@@ -24,11 +24,15 @@ def et():
     return et_b200
 
 
-def make_layer(orc, d, dff, sparsity, seed, bernoulli=True, bias_std=0.02):
+def make_layer(orc, d, dff, sparsity, seed, bernoulli=True, bias_std=0.02, unit_scale=False):
+    """unit_scale: weight std 1/sqrt(kept inputs) instead of 0.02, so that every sub-layer's output is as large as
+    the residual it is added to (with std 0.02 the attention and FFN branches are a few per cent of the residual
+    and an error in them hides below the tolerance)."""
     shapes = {"q": (d, d), "k": (d, d), "v": (d, d), "o": (d, d), "ffn1": (d, dff), "ffn2": (dff, d)}
     lin = {}
     for i, (name, (K, N)) in enumerate(shapes.items()):
-        rp, ro, data, bias = util.make_tile_linear(orc, K, N, sparsity, seed + 10 * i, bernoulli, bias_std)
+        std = 1.0 / np.sqrt(K * max(1.0 - sparsity, 1e-3)) if unit_scale else 0.02
+        rp, ro, data, bias = util.make_tile_linear(orc, K, N, sparsity, seed + 10 * i, bernoulli, bias_std, std=std)
         lin[name] = (rp, ro, data, bias, N, K)
     g = [(1.0 + util.weights(seed + 100 + j, (d,), 0.1).astype(np.float32)).astype(np.float16) for j in range(2)]
     b = [util.weights(seed + 110 + j, (d,), 0.1) for j in range(2)]
@@ -219,6 +223,68 @@ def test_encoder_prune_v_and_qkv(et, orc):
         enc.run_batch(out, dev(X), [S] * B, scratch)
         torch.cuda.synchronize()
         util.assert_close(host(out), oracle(prune_qk), what=f"Encoder_prune prune_qk={prune_qk}")
+
+
+def test_encoder_kinds_with_unit_scale_weights(et, orc):
+    """Every encoder kind with weights scaled so that the attention and FFN branches are as large as the residual:
+    the operand pitches and head windows that the layer hands to the attention kernels (fused Q|K|V buffers,
+    compact row-pruned operands, materialised scores) all have to be right for this to pass."""
+    d, H, dff, S = 256, 4, 1024, 128
+    lin, ln = make_layer(orc, d, dff, 0.5, seed=70, unit_scale=True)
+    ol = orc_lin(lin)
+    lnp = (ln[0][0], ln[0][1], ln[1][0], ln[1][1])
+    lens = [128, 37, 90]
+    T = sum(lens)
+    X = util.activations(71, (T, d))
+    want = orc.encoder_layer(X, ol, ln, lens, d, H)
+    tol = dict(max_abs=4e-2, mean_abs=4e-3)   # fp16 storage of O(1) intermediates through five fused stages
+    scratch = torch.zeros(et.encoder_batch_buffer_size(et.KIND_LENGTH, d, 3 * S, 3, S, H) // 2, dtype=torch.float16, device="cuda")
+    # tile layer, variable lengths (tensor-core attention, fused Q|K|V)
+    enc = build_encoder(et, et.KIND_LENGTH, lin, ln, d, S, H, T)
+    out = torch.zeros((T, d), dtype=torch.float16, device="cuda")
+    enc.run_batch(out, dev(X), lens, scratch)
+    torch.cuda.synchronize()
+    util.assert_close(host(out), want, what="unit-scale weights, varlen", **tol)
+    # padded with key padding, on the fly and through materialised scores
+    Xp = np.zeros((3 * S, d), dtype=np.float16)
+    rows = np.concatenate([np.arange(b * S, b * S + lens[b]) for b in range(3)])
+    Xp[rows] = X
+    for mat in (False, True):
+        enc.set_materialize_scores(mat)
+        outp = torch.zeros((3 * S, d), dtype=torch.float16, device="cuda")
+        enc.run_batch(outp, dev(Xp), [S] * 3, scratch, valid_lens=lens)
+        torch.cuda.synchronize()
+        util.assert_close(host(outp)[rows], want, what=f"unit-scale weights, padded, materialised scores {mat}", **tol)
+    # row-pruned V, and row-pruned Q, K and V
+    row_id = orc.gen_sparse_row_mat(d, 0.5, seed=72, nhead=H)
+    hp = orc.head_ptr(row_id, H, d)
+    std = 1.0 / np.sqrt(d)
+    Wr = {n: util.weights(300 + i, (len(row_id), d), std) for i, n in enumerate("qkv")}
+    br = {n: util.weights(310 + i, (len(row_id),), 0.02) for i, n in enumerate("qkv")}
+    Xf = X.astype(np.float32)
+    for prune_qk in (False, True):
+        if prune_qk:
+            q, k = orc.row_linear(Xf, Wr["q"], br["q"]), orc.row_linear(Xf, Wr["k"], br["k"])
+        else:
+            q, k = orc.tile_linear(Xf, *ol["q"][:4], ol["q"][4]), orc.tile_linear(Xf, *ol["k"][:4], ol["k"][4])
+        v = orc.row_linear(Xf, Wr["v"], br["v"])
+        z = orc.attention(q, k, v, lens, d, H, qk_head_ptr=hp if prune_qk else None, v_col_id=row_id, v_head_ptr=hp)
+        a = orc.tile_linear(z, *ol["o"][:4], ol["o"][4])
+        h1 = orc.skip_layernorm(a, Xf, *ln[0])
+        f = orc.tile_linear(h1, *ol["ffn1"][:4], ol["ffn1"][4], gelu=True)
+        wantp = orc.skip_layernorm(orc.tile_linear(f, *ol["ffn2"][:4], ol["ffn2"][4]), h1, *ln[1])
+        w = tile_weights(et, lin, T)
+        rv = et.RowWeight(d, d, T, Wr["v"], row_id, br["v"], H)
+        if prune_qk:
+            encp = et.Encoder(et.KIND_PRUNE_QKV, d, S, H, None, et.RowWeight(d, d, T, Wr["q"], row_id, br["q"], H),
+                              et.RowWeight(d, d, T, Wr["k"], row_id, br["k"], H), rv, w["o"], w["ffn1"], w["ffn2"], lnp)
+        else:
+            encp = et.Encoder(et.KIND_PRUNE, d, S, H, None, w["q"], w["k"], rv, w["o"], w["ffn1"], w["ffn2"], lnp)
+        outq = torch.zeros((T, d), dtype=torch.float16, device="cuda")
+        encp.run_batch(outq, dev(X), lens, scratch)
+        torch.cuda.synchronize()
+        util.assert_close(host(outq), wantp, what=f"unit-scale weights, row-pruned, prune_qk={prune_qk}", **tol)
+        encp.check()
 
 
 def test_bert_large_layer_properties_at_full_slab(et, orc):
