@@ -399,7 +399,21 @@ def reference_configs(torch, ref, orc, tile_stack, stream, dev):
                  "what": "32 x 256 tokens; Q/K tile-pruned 50 % (the reference's Encoder_prune row-prunes V only), V row-pruned "
                          "50 %, output projection and FFN tile-pruned 75 %; its pruned-attention kernel as shipped computes "
                          "the attention and never stores it, which only shortens its time"}
-    del xs, ys, bufs
+    xr = [dev(sequence_inputs(6000 + 100 * i, B, S, d)) for i in range(8)]
+    wr = [dev((np.random.default_rng(7290 + i).standard_normal((nnz, d), dtype=np.float32) * 0.02).astype(np.float16)) for i in range(8)]
+    yr = [torch.zeros((T, nnz), dtype=torch.float16, device="cuda") for _ in range(8)]
+    k[0] = 0
+
+    def row_fn():
+        i = k[0] % 8
+        k[0] += 1
+        rc = ref.ref_row_spmm(vp(yr[i].data_ptr()), vp(xr[i].data_ptr()), vp(wr[i].data_ptr()), vp(vbd.data_ptr()), T, nnz, d, sp)
+        assert rc == 0, "reference row linear failed"
+    ms_r = time_loop(torch, row_fn, 200, 16, stream)
+    out["c3_row_linear"] = {"us": ms_r * 1e3, "tflops": 2.0 * T * len(ids) * d / (ms_r * 1e-3) / 1e12,
+                            "what": f"the reference's row-pruned launcher alone (bias fill + cuBLAS GEMM), {T} tokens, {len(ids)} of {d} "
+                                    "output features kept, eight weight/activation sets rotated"}
+    del xs, ys, bufs, xr, wr, yr
 
     # c4: 12 layers, 64 sequences with lengths U[32,512] rounded UP to 16 (the reference's kernels need multiples of
     # 16), scores GEMM + shared-QK attention per sequence; against the same batch padded to 512.
@@ -539,7 +553,21 @@ def native_configs(torch, et, stream, pk):
     ms = time_loop(torch, prune_fn, 90, 9, stream)
     out["c3"] = {"us_per_layer": ms * 1e3, "sequences_per_s": B / (ms * 1e-3), "instances_rotated": insts,
                  "what": "32 x 256 tokens; Q, K and V row-pruned to half of every head, output projection and FFN tile-pruned 75 %"}
-    del models, xs, ys
+    # the row-pruned linear alone at this shape (the reference runs cuBLAS there)
+    rws = [row_weight(et.gen_sparse_row_mat(d, 0.5, 7290 + i, nhead=H)) for i in range(8)]
+    yr = [torch.zeros((T, rws[0].nrow), dtype=torch.float16, device="cuda") for _ in range(8)]
+    xr = [dev(sequence_inputs(6000 + 100 * i, B, S, d)) for i in range(8)]
+    k[0] = 0
+
+    def row_fn():
+        i = k[0] % 8
+        k[0] += 1
+        rws[i].run(yr[i], xr[i], stream=stream)
+    ms_r = time_loop(torch, row_fn, 200, 16, stream)
+    out["c3_row_linear"] = {"us": ms_r * 1e3, "tflops": 2.0 * T * rws[0].row_id_size * d / (ms_r * 1e-3) / 1e12,
+                            "what": f"row-pruned linear alone, {T} tokens, {rws[0].row_id_size} of {d} output features kept, in_feat {d}, "
+                                    "eight weight/activation sets rotated"}
+    del models, xs, ys, rws, yr, xr
 
     # c4: 12 layers, 64 sequences of length U[32,512], packed (length-driven tiling) against padded to 512
     lens = np.random.default_rng(4242).integers(32, 513, size=64).tolist()

@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libet_b200.so")
-SOURCES = ["error.cu", "layernorm.cu", "softmax.cu", "tile_gemm.cu", "attention.cu", "attention_tc.cu", "formats.cu",
+SOURCES = ["error.cu", "layernorm.cu", "softmax.cu", "tile_gemm.cu", "attention.cu", "attention_tc.cu", "expand.cu", "formats.cu",
            "encoder.cu", "api.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
          "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-shared"]

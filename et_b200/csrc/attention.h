@@ -26,6 +26,11 @@ int attention_prepare_device();
 int qk_scores_launch(half* S, const half* Q, const half* K, int batch, int L, int d_model, int nhead,
                      cudaStream_t st, int pitch = 0);
 
+// dst[o][t][p] = inv[o][p] >= 0 ? src[o][t][inv[o][p]] : 0 for n <= 3 operands in one launch: compact row-pruned
+// activations back at their original feature positions, zeros elsewhere (d a multiple of 8).
+int expand_rows_launch(int n, const half* const* src, const int* src_pitch, half* const* dst, const int* dst_pitch,
+                       const int* const* inv, int d, int T, cudaStream_t st);
+
 // Same result as the on-the-fly form for one sequence, through scores held in a device array that is part
 // of the library image (no allocation). seq_len*seq_len*nhead is limited to 16*512*512.
 int attention_static_scores(half* Z, const half* Q, const half* K, const half* V, const half* mask, int seq_len,

@@ -30,11 +30,13 @@ struct RowWeight {
     TileWeight* tw = nullptr;
     int* d_row_id = nullptr;
     int* d_head_ptr = nullptr;
+    int* d_inv = nullptr;   // [out_feat]: compact column of an original feature, -1 where it was pruned
     std::vector<int> h_head_ptr;
     ~RowWeight() {
         tile_weight_free(tw);
         cudaFree(d_row_id);
         cudaFree(d_head_ptr);
+        cudaFree(d_inv);
     }
 };
 
@@ -86,6 +88,12 @@ static int row_weight_create(RowWeight** out, int in_feat, int out_feat, int siz
         return fail(ET_ERR_CUDA, "row weight: cudaMalloc failed");
     cudaMemcpy(w->d_row_id, row_id, sizeof(int) * row_id_size, cudaMemcpyHostToDevice);
     cudaMemcpy(w->d_head_ptr, w->h_head_ptr.data(), sizeof(int) * (nhead + 1), cudaMemcpyHostToDevice);
+    {
+        std::vector<int> inv((size_t)(out_feat + 7) / 8 * 8, -1);
+        for (int i = 0; i < row_id_size; ++i) inv[row_id[i]] = i;
+        if (cudaMalloc(&w->d_inv, sizeof(int) * inv.size()) != cudaSuccess) return fail(ET_ERR_CUDA, "row weight: cudaMalloc failed");
+        cudaMemcpy(w->d_inv, inv.data(), sizeof(int) * inv.size(), cudaMemcpyHostToDevice);
+    }
     *out = w.release();
     return ET_OK;
 }
@@ -166,6 +174,8 @@ struct Encoder {
     TileWeight* lin[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};  // q k v o mlp1 mlp2
     TileWeight* qkv = nullptr;   // Q|K|V as one weight: one launch, one staging of the activations per CTA
     int qkv_cols[3] = {0, 0, 0}; // output columns of the three parts inside the fused result
+    bool expand_pruned = false;  // row-pruned operands are expanded to their original positions (zeros where pruned)
+                                 // and attention runs on the tensor-core kernel
     RowWeight* rq = nullptr; RowWeight* rk = nullptr; RowWeight* rv = nullptr;
     half* d_ln[4] = {nullptr, nullptr, nullptr, nullptr};  // gamma1 beta1 gamma2 beta2
     half* d_mask = nullptr;                                // [seq_len x seq_len] additive, may be null
@@ -247,7 +257,41 @@ static int encoder_forward(Encoder* e, half* out, const half* in, half* scratch,
     int rc;
     int q_pitch = e->d_model, v_pitch = e->d_model;
     const int *qk_hp = nullptr, *v_hp = nullptr, *v_id = nullptr;
-    if (e->qkv) {
+    if (e->qkv && e->expand_pruned) {
+        // Row-pruned operands. One launch writes the compact Q | K | V side by side; one bandwidth-bound pass puts
+        // the row-pruned ones back at their original feature positions with zeros where a feature was pruned; the
+        // tensor-core attention kernel then runs on dense heads of 64: a zero column adds nothing to Q K^T, and a
+        // zero column of V gives a zero column of the result, which is the scatter with zero fill that the pruned
+        // attention means (kernels/attention.cu:242-248).
+        const int P = e->qkv_cols[0] + e->qkv_cols[1] + e->qkv_cols[2];
+        const int d = e->d_model;
+        half* b4 = scratch + 4 * td;
+        if (e->kind == kPruneQKV) {
+            // compact result in buffers 3-4 (P <= 2 d_model), expanded Q | K | V over buffers 0-2
+            half* comp = b3;
+            if ((rc = tile_linear_run(e->qkv, comp, in, T, 0, st))) return rc;
+            const half* src[3] = {comp, comp + e->qkv_cols[0], comp + e->qkv_cols[0] + e->qkv_cols[1]};
+            const int sp[3] = {P, P, P}, dp[3] = {3 * d, 3 * d, 3 * d};
+            half* dst[3] = {b0, b0 + d, b0 + 2 * d};
+            const int* inv[3] = {e->rq->d_inv, e->rk->d_inv, e->rv->d_inv};
+            if ((rc = expand_rows_launch(3, src, sp, dst, dp, inv, d, T, st))) return rc;
+            q_pitch = v_pitch = 3 * d;
+            b1 = b0 + d;
+            b2 = b0 + 2 * d;
+        } else {
+            // Q and K are dense already (inside the fused result); only V is expanded, into buffer 4
+            if ((rc = tile_linear_run(e->qkv, b0, in, T, 0, st))) return rc;
+            const half* src[1] = {b0 + e->qkv_cols[0] + e->qkv_cols[1]};
+            const int sp[1] = {P}, dp[1] = {d};
+            half* dst[1] = {b4};
+            const int* inv[1] = {e->rv->d_inv};
+            if ((rc = expand_rows_launch(1, src, sp, dst, dp, inv, d, T, st))) return rc;
+            q_pitch = P;
+            v_pitch = d;
+            b1 = b0 + e->qkv_cols[0];
+            b2 = b4;
+        }
+    } else if (e->qkv) {
         // fused: one launch writes Q | K | V side by side, [T x (q + k + v columns)] over the first three scratch
         // buffers (row-pruned parts are compact, so the three widths may differ)
         if ((rc = tile_linear_run(e->qkv, b0, in, T, 0, st))) return rc;
@@ -514,6 +558,7 @@ int et_encoder_prune_create(et_encoder** out, int d_model, int seq_len, int nhea
         if ((rc = et::tile_weight_concat(&e->qkv, parts, 3, 0))) return rc;
         e->qkv_cols[0] = e->qkv_cols[1] = d_model;
         e->qkv_cols[2] = e->rv->nrow;
+        e->expand_pruned = d_model / nheads == 64 && e->rv->out_feat == d_model;   // the tensor-core kernel's head width
     }
     return finish_create(out, e);
 }
@@ -546,6 +591,8 @@ int et_encoder_prune_qkv_create(et_encoder** out, int d_model, int seq_len, int 
         const et::TileWeight* parts[3] = {e->rq->tw, e->rk->tw, e->rv->tw};
         if ((rc = et::tile_weight_concat(&e->qkv, parts, 3, 0))) return rc;
         e->qkv_cols[0] = e->rq->nrow; e->qkv_cols[1] = e->rk->nrow; e->qkv_cols[2] = e->rv->nrow;
+        e->expand_pruned = d_model / nheads == 64 && e->rq->out_feat == d_model && e->rk->out_feat == d_model &&
+                           e->rv->out_feat == d_model && e->rq->nrow + e->rk->nrow + e->rv->nrow <= 2 * d_model;
     }
     return finish_create(out, e);
 }
