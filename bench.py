@@ -615,6 +615,8 @@ def main():
     ap.add_argument("--layers", type=int, default=LARGE["layers"], help="debugging only: anything but 24 is not the named workload")
     ap.add_argument("--batch", type=int, default=LARGE["B"], help="debugging only: global batch (256 is the named workload)")
     ap.add_argument("--seq", type=int, default=LARGE["S"], help="debugging only")
+    ap.add_argument("--ln-fusion", action="store_true", help="debugging only: the layer stack's optional form with the LayerNorms folded "
+                    "into the linears (5 launches per layer instead of 7; slower on B200, off by default in the library)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the bandwidth legs")
     args = ap.parse_args()
@@ -649,6 +651,10 @@ def main():
 
     with ClockSampler(local_rank) as cs:
         model, lin0 = build_model(et, c, T)
+        if args.ln_fusion:
+            model.set_layernorm_fusion(True)
+        fused = model.layernorm_fused
+        launches_per_layer = 5 if fused else 7
         model.reserve(T, Br, c["S"])
         X = sequence_inputs(rank * Br, Br, c["S"], d)
         x = torch.from_numpy(X).cuda()
@@ -845,9 +851,13 @@ def main():
                                    "maximum over ranks; the median repetition is reported",
                          "l2": "inputs larger than L2: the shard's activations (input, scratch of five token x hidden buffers, output) "
                                "are several times the 126 MB L2 and every layer streams them"},
-              "clocks": clocks, "e2e": e2e, "gpu_launches": 7 * c["layers"] * args.steps * R,
-              "launches_per_step": f"{7 * c['layers']}: per layer fused Q|K|V tile GEMM, attention, output tile GEMM, LayerNorm, FFN1 tile "
-                                   "GEMM (GELU), FFN2 tile GEMM, LayerNorm; all layers replayed as one CUDA graph",
+              "clocks": clocks, "e2e": e2e, "gpu_launches": (launches_per_layer * c["layers"] + (1 if fused else 0)) * args.steps * R,
+              "launches_per_step": (f"{5 * c['layers'] + 1}: per layer fused Q|K|V tile GEMM, attention, output tile GEMM (+ residual, row sums), "
+                                    "FFN1 tile GEMM (normalises its input, GELU), FFN2 tile GEMM (+ LayerNorm of the residual, row sums); one "
+                                    "LayerNorm at the end; all replayed as one CUDA graph") if fused else
+                                   (f"{7 * c['layers']}: per layer fused Q|K|V tile GEMM, attention, output tile GEMM, LayerNorm, FFN1 tile "
+                                    "GEMM (GELU), FFN2 tile GEMM, LayerNorm; all layers replayed as one CUDA graph"),
+              "layernorm_folded_into_linears": fused,
               "roofline": roofline, "roofline_attention": roofline_attention,
               "model_tflops": layer_fl * c["layers"] * world / (ms * 1e-3) / 1e12, "gather_check": gather_check,
               "device_error_words": 0}

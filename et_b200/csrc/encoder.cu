@@ -178,6 +178,7 @@ struct Encoder {
                                  // and attention runs on the tensor-core kernel
     RowWeight* rq = nullptr; RowWeight* rk = nullptr; RowWeight* rv = nullptr;
     half* d_ln[4] = {nullptr, nullptr, nullptr, nullptr};  // gamma1 beta1 gamma2 beta2
+    std::vector<half> h_ln[4];                             // the same on the host (folded into weights by the layer stack)
     half* d_mask = nullptr;                                // [seq_len x seq_len] additive, may be null
     int* d_lens = nullptr; int lens_cap = 0;               // cu_seqlens (batch+1) then valid_lens (batch)
     bool materialize_scores = false;
@@ -242,6 +243,7 @@ static int encoder_common(Encoder* e, int d_model, int seq_len, int nheads, half
     for (int i = 0; i < 4; ++i) {
         int rc = upload_half(&e->d_ln[i], src[i], d_model);
         if (rc) return rc;
+        e->h_ln[i].assign(src[i], src[i] + d_model);
     }
     if (mask) return upload_half(&e->d_mask, mask, (size_t)seq_len * seq_len);
     return ET_OK;
@@ -349,18 +351,133 @@ struct Model {
     std::vector<Replay> replays;
     bool use_graphs = true;
     StreamBridge bridge;
+    // LayerNorm folded into the linears (tile and length layers): per layer the FFN1 weight folded with the layer's
+    // first LayerNorm, the fused Q|K|V weight folded with the PREVIOUS layer's second LayerNorm, fp32 copies of
+    // the four LayerNorm vectors; per row the partial sums that the output projection and FFN2 leave behind.
+    struct Fused {
+        TileWeight* ffn1 = nullptr;
+        TileWeight* qkv = nullptr;
+        float* lnf[4] = {nullptr, nullptr, nullptr, nullptr};
+        int np1 = 0, np2 = 0;   // partial-sum slots per row of the output projection / of FFN2
+    };
+    std::vector<Fused> fused;
+    bool fuse_ln = false;
+    float* stats1 = nullptr; float* stats2 = nullptr; size_t stats_floats = 0;
     void drop_replays() {
         for (auto& r : replays)
             if (r.exec) cudaGraphExecDestroy(r.exec);
         replays.clear();
     }
+    void drop_fused() {
+        for (auto& f : fused) {
+            tile_weight_free(f.ffn1);
+            tile_weight_free(f.qkv);
+            for (float* p : f.lnf) cudaFree(p);
+        }
+        fused.clear();
+        fuse_ln = false;
+    }
     ~Model() {
         drop_replays();
+        drop_fused();
         for (auto* e : layers) delete e;
         cudaFree(scratch);
         cudaFree(d_lens);
+        cudaFree(stats1);
+        cudaFree(stats2);
     }
 };
+
+int layernorm_launch(half* x, const half* s, const half* g, const half* b, int num, int size, cudaStream_t st);
+
+// Builds the folded weights. Returns ET_OK with fuse_ln left false when the stack is not eligible (a row-pruned
+// layer, or a layer without the fused Q|K|V weight): such stacks run layer by layer with separate LayerNorms.
+static int model_prepare_fusion(Model* m) {
+    m->drop_fused();
+    for (const Encoder* e : m->layers)
+        if ((e->kind != kTile && e->kind != kLength) || !e->qkv || (e->d_model & 7)) return ET_OK;
+    m->fused.resize(m->layers.size());
+    for (size_t l = 0; l < m->layers.size(); ++l) {
+        Encoder* e = m->layers[l];
+        Model::Fused& f = m->fused[l];
+        int rc = tile_weight_fold(&f.ffn1, e->lin[4], e->h_ln[0].data(), e->h_ln[1].data());
+        if (rc == ET_OK && l > 0) {
+            const Encoder* pe = m->layers[l - 1];
+            rc = tile_weight_fold(&f.qkv, e->qkv, pe->h_ln[2].data(), pe->h_ln[3].data());
+        }
+        if (rc) { m->drop_fused(); return rc; }
+        for (int i = 0; i < 4; ++i) {
+            std::vector<float> v(e->d_model);
+            for (int k = 0; k < e->d_model; ++k) v[k] = __half2float(e->h_ln[i][k]);
+            if (cudaMalloc(&f.lnf[i], v.size() * sizeof(float)) != cudaSuccess) { m->drop_fused(); return fail(ET_ERR_CUDA, "model: cudaMalloc failed"); }
+            cudaMemcpy(f.lnf[i], v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice);
+        }
+        f.np1 = 2 * tile_weight_chunks(e->lin[3]);
+        f.np2 = 2 * tile_weight_chunks(e->lin[5]);
+    }
+    m->fuse_ln = true;
+    return ET_OK;
+}
+
+// The stack with its LayerNorms folded into the linears. Per layer: fused Q|K|V (normalising its input in the
+// epilogue from layer 1 on), attention, output projection + residual -> y1 and its row sums, FFN1 (normalises y1 in
+// the epilogue, GELU), FFN2 + LayerNorm(y1) as residual -> y2 and its row sums into `out`; the next layer reads
+// `out` un-normalised. One plain LayerNorm of `out` ends the stack. 5 launches per layer instead of 7.
+static int model_forward_fused(Model* m, half* out, const half* in, int T, const int* cu, const int* vl, int batch,
+                               int uniform_len, cudaStream_t st, int max_len) {
+    half* scratch = m->scratch;
+    const half* yprev = in;
+    int rc;
+    for (size_t l = 0; l < m->layers.size(); ++l) {
+        Encoder* e = m->layers[l];
+        const Model::Fused& f = m->fused[l];
+        const int d = e->d_model;
+        const size_t td = (size_t)T * d;
+        half* b0 = scratch; half* b3 = scratch + 3 * td;
+        half* b1 = scratch + td;
+        if (l == 0) {
+            if ((rc = tile_linear_run(e->qkv, b0, in, T, 0, st))) return rc;
+        } else {
+            GemmFusion fz;
+            fz.mode = 1; fz.stats_in = m->stats2; fz.np_in = m->fused[l - 1].np2;
+            if ((rc = tile_linear_run(f.qkv, b0, yprev, T, 0, st, nullptr, &fz))) return rc;
+        }
+        const half* scores = nullptr;
+        if (e->kind == kLength && e->materialize_scores && !cu) {
+            half* sbuf = scratch + 5 * td;
+            if ((rc = qk_scores_launch(sbuf, b0, b0 + d, batch, uniform_len, d, e->nheads, st, 3 * d))) return rc;
+            scores = sbuf;
+        }
+        if ((rc = attention_launch(b3, b0, b0 + d, b0 + 2 * d, scores, 3 * d, 3 * d, nullptr, nullptr, nullptr, e->d_mask,
+                                   e->seq_len, cu, vl, batch, uniform_len, T, d, e->nheads, st, max_len)))
+            return rc;
+        {   // y1 = Z Wo^T + bo + residual
+            GemmFusion fz;
+            fz.resid = yprev; fz.stats_out = m->stats1; fz.np_out = f.np1;
+            if (l == 0) {
+                fz.mode = 2;
+            } else {
+                const Model::Fused& pf = m->fused[l - 1];
+                fz.mode = 3; fz.stats_src = m->stats2; fz.np_src = pf.np2; fz.gamma_s = pf.lnf[2]; fz.beta_s = pf.lnf[3];
+            }
+            if ((rc = tile_linear_run(e->lin[3], b0, b3, T, 0, st, nullptr, &fz))) return rc;
+        }
+        {   // F = gelu(LN1(y1) W1^T + b1)
+            GemmFusion fz;
+            fz.mode = 1; fz.stats_in = m->stats1; fz.np_in = f.np1;
+            if ((rc = tile_linear_run(f.ffn1, b1, b0, T, 1, st, nullptr, &fz))) return rc;
+        }
+        {   // y2 = F W2^T + b2 + LN1(y1)
+            GemmFusion fz;
+            fz.mode = 3; fz.resid = b0; fz.stats_src = m->stats1; fz.np_src = f.np1; fz.gamma_s = f.lnf[0]; fz.beta_s = f.lnf[1];
+            fz.stats_out = m->stats2; fz.np_out = f.np2;
+            if ((rc = tile_linear_run(e->lin[5], out, b1, T, 0, st, nullptr, &fz))) return rc;
+        }
+        yprev = out;
+    }
+    const Encoder* last = m->layers.back();
+    return layernorm_launch(out, nullptr, last->d_ln[2], last->d_ln[3], T, last->d_model, st);
+}
 
 static size_t model_scratch_halfs(const Model* m, int total_tokens, int batch, int max_len) {
     size_t need = 0;
@@ -374,6 +491,7 @@ static size_t model_scratch_halfs(const Model* m, int total_tokens, int batch, i
 
 static int model_forward(Model* m, half* out, const half* in, int T, const int* cu, const int* vl, int batch,
                          int uniform_len, cudaStream_t st, int max_len) {
+    if (m->fuse_ln) return model_forward_fused(m, out, in, T, cu, vl, batch, uniform_len, st, max_len);
     const half* x = in;
     for (Encoder* e : m->layers) {
         // a layer may write over its own input (the input is consumed before the last two launches write `out`)
@@ -802,6 +920,16 @@ int et_model_create(et_model** out, et_encoder* const* layers, int n_layers) {
     return ET_OK;
 }
 
+int et_model_set_layernorm_fusion(et_model* model, int on) {
+    ET_REQUIRE(model && model->m, "et_model_set_layernorm_fusion: null model");
+    et::Model* m = model->m;
+    m->drop_replays();
+    if (!on) { m->drop_fused(); return ET_OK; }
+    return et::model_prepare_fusion(m);
+}
+
+int et_model_layernorm_fused(const et_model* model) { return model && model->m && model->m->fuse_ln ? 1 : 0; }
+
 int et_model_destroy(et_model* model) {
     if (model) { delete model->m; delete model; }
     return ET_OK;
@@ -816,6 +944,14 @@ int et_model_check(et_model* model, int* code) {
         const int rc = encoder_check(e, code);
         if (rc) return rc;
     }
+    for (const auto& f : model->m->fused)
+        for (et::TileWeight* w : {f.ffn1, f.qkv}) {
+            if (!w) continue;
+            int c = 0;
+            const int rc = et::tile_weight_error(w, &c);
+            if (rc) return rc;
+            if (c && !*code) *code = c;
+        }
     if (*code) {
         et::set_error("layer stack: device wait %d gave up", *code);
         return ET_ERR_DEVICE_TIMEOUT;
@@ -836,12 +972,23 @@ int et_model_reserve(et_model* model, int total_tokens, int batch, int max_len) 
     ET_REQUIRE(total_tokens >= 0 && batch >= 0 && max_len >= 0, "et_model_reserve: negative size");
     et::Model* m = model->m;
     const size_t need = et::model_scratch_halfs(m, total_tokens, batch, max_len);
-    if (need <= m->scratch_halfs) return ET_OK;
-    m->drop_replays();
-    cudaFree(m->scratch);
-    m->scratch = nullptr; m->scratch_halfs = 0;
-    if (cudaMalloc(&m->scratch, need * sizeof(half)) != cudaSuccess) return et::fail(ET_ERR_CUDA, "et_model_reserve: cudaMalloc failed");
-    m->scratch_halfs = need;
+    size_t need_stats = 0;
+    for (const auto& f : m->fused) need_stats = std::max(need_stats, (size_t)total_tokens * std::max(f.np1, f.np2) * 2);
+    if (need > m->scratch_halfs) {
+        m->drop_replays();
+        cudaFree(m->scratch);
+        m->scratch = nullptr; m->scratch_halfs = 0;
+        if (cudaMalloc(&m->scratch, need * sizeof(half)) != cudaSuccess) return et::fail(ET_ERR_CUDA, "et_model_reserve: cudaMalloc failed");
+        m->scratch_halfs = need;
+    }
+    if (need_stats > m->stats_floats) {
+        m->drop_replays();
+        cudaFree(m->stats1); cudaFree(m->stats2);
+        m->stats1 = m->stats2 = nullptr; m->stats_floats = 0;
+        if (cudaMalloc(&m->stats1, need_stats * sizeof(float)) != cudaSuccess || cudaMalloc(&m->stats2, need_stats * sizeof(float)) != cudaSuccess)
+            return et::fail(ET_ERR_CUDA, "et_model_reserve: cudaMalloc failed");
+        m->stats_floats = need_stats;
+    }
     return ET_OK;
 }
 
@@ -881,7 +1028,9 @@ int et_model_run_batch(et_model* model, void* out, const void* in, const int* se
     const bool capturing = cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone;
     if (capturing) {
         // inside the caller's own capture nothing may be allocated or uploaded from a temporary
-        ET_REQUIRE(et::model_scratch_halfs(m, T, batch, max_len) <= m->scratch_halfs,
+        size_t need_stats = 0;
+        for (const auto& f : m->fused) need_stats = std::max(need_stats, (size_t)T * std::max(f.np1, f.np2) * 2);
+        ET_REQUIRE(et::model_scratch_halfs(m, T, batch, max_len) <= m->scratch_halfs && need_stats <= m->stats_floats,
                    "et_model_run_batch: call et_model_reserve before capturing");
         ET_REQUIRE(uniform && !valid_lens_host, "et_model_run_batch: only equal-length batches can run inside the caller's capture");
     } else {

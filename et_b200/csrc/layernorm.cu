@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(256, (CH <= 4 ? 3 : 1)) skip_layernorm_vec(hal
             const int c = lane + 32 * i;
             if (c < nchunk) {
                 xv[i] = xr[c];
-                sv[i] = __ldcs(sr + c);
+                sv[i] = skip ? __ldcs(sr + c) : make_uint4(0u, 0u, 0u, 0u);   // no residual: plain LayerNorm of the row
             }
         }
         float v[CH][8];
@@ -105,16 +105,16 @@ __global__ void __launch_bounds__(256) skip_layernorm_generic(half* __restrict__
         half* x = in_out + (size_t)row * size;
         const half* s = skip + (size_t)row * size;
         float sum = 0.f;
-        for (int i = lane; i < size; i += 32) sum += __half2float(x[i]) + __half2float(s[i]);
+        for (int i = lane; i < size; i += 32) sum += __half2float(x[i]) + (skip ? __half2float(s[i]) : 0.f);
         const float mean = warp_sum(sum) * inv_n;
         float sq = 0.f;
         for (int i = lane; i < size; i += 32) {
-            const float d = __half2float(x[i]) + __half2float(s[i]) - mean;
+            const float d = __half2float(x[i]) + (skip ? __half2float(s[i]) : 0.f) - mean;
             sq += d * d;
         }
         const float rstd = rsqrtf(warp_sum(sq) * inv_n + 1e-6f);
         for (int i = lane; i < size; i += 32) {
-            const float v = __half2float(x[i]) + __half2float(s[i]);
+            const float v = __half2float(x[i]) + (skip ? __half2float(s[i]) : 0.f);
             x[i] = __float2half_rn((v - mean) * rstd * __half2float(gamma[i]) +
                                    __half2float(beta[i]));
         }
@@ -123,22 +123,28 @@ __global__ void __launch_bounds__(256) skip_layernorm_generic(half* __restrict__
 
 }  // namespace et
 
+namespace et {
+// in_out <- LN(in_out + skip) * gamma + beta; skip == nullptr leaves the residual out (the layer stack's last
+// LayerNorm when the others are folded into the linears).
+int layernorm_launch(half* x, const half* s, const half* g, const half* b, int num, int size, cudaStream_t st);
+}
+
 extern "C" int et_skip_layernorm(void* in_out, const void* skip, const void* gamma,
                                  const void* beta, int num, int size, void* stream) {
-    using namespace et;
     ET_REQUIRE(in_out && skip && gamma && beta, "et_skip_layernorm: null pointer");
     ET_REQUIRE(num >= 0 && size > 0, "et_skip_layernorm: bad dimensions");
+    return et::layernorm_launch(static_cast<half*>(in_out), static_cast<const half*>(skip), static_cast<const half*>(gamma),
+                                static_cast<const half*>(beta), num, size, static_cast<cudaStream_t>(stream));
+}
+
+int et::layernorm_launch(half* x, const half* s, const half* g, const half* b, int num, int size, cudaStream_t st) {
+    using namespace et;
     if (num == 0) return ET_OK;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    half* x = static_cast<half*>(in_out);
-    const half* s = static_cast<const half*>(skip);
-    const half* g = static_cast<const half*>(gamma);
-    const half* b = static_cast<const half*>(beta);
     const int warps_needed = num;
     int blocks = (warps_needed + 7) / 8;
     const int cap = sm_count() * 8;  // 8 blocks of 8 warps per SM: the full 64 resident warps
     if (blocks > cap) blocks = cap;
-    const bool vec = size % 8 == 0 && size <= 2048 && aligned16(x) && aligned16(s) &&
+    const bool vec = size % 8 == 0 && size <= 2048 && aligned16(x) && (!s || aligned16(s)) &&
                      aligned16(g) && aligned16(b);
     if (vec) {
         const int ch = (size / 8 + 31) / 32;

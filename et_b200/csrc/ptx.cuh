@@ -78,6 +78,10 @@ __device__ __forceinline__ void tma_store_commit() {
 __device__ __forceinline__ void tma_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
+// All but the most recent store group of this thread have finished reading shared memory.
+__device__ __forceinline__ void tma_store_wait_read1() {
+    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes,
                                           uint64_t* bar) {

@@ -68,6 +68,7 @@ struct GemmParams {
     int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, stages, a_slots, epi_bufs, gelu;
     int* err;
     uint2 first[kDirInParams];   // dir[chunk][0] for chunk < kDirInParams: no global load before the first TMA
+    GemmFusion fz;           // LayerNorm folded into the epilogue (modes 1-3 of the kernel template)
     long long* prof;         // optional per-role clock64 stamps of CTA (0,0) (ET_GEMM_PROFILE builds only)
 };
 
@@ -170,6 +171,103 @@ __device__ __forceinline__ void epi_write(uint8_t* buf, int lane, const uint4 (&
     for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(prow + ((c ^ x) << 4)) = ov[c];
 }
 
+// ---- LayerNorm folded into the epilogue (the layer stack's fused path) --------------------------------------------
+// A residual-add + LayerNorm between two linears costs two passes over the activations. Folded: the linear BEFORE
+// the LayerNorm adds the residual in its epilogue, writes the un-normalised sum y and, per row and CTA, the partial
+// sums (sum y, sum y^2) of its columns (modes 2 and 3); the linear AFTER it reads y with gamma multiplied into its
+// weights and applies mean and 1/std per row in its epilogue (mode 1):
+//     LN(y) W^T + b = r (y (gamma o W)^T - mu c) + d,   c_n = sum_k gamma_k W_nk,  d_n = sum_k beta_k W_nk + b_n.
+// Partial sums are written to their own slot per (row, column chunk, warp of the row quarter) and added up by the
+// reader in slot order: no atomics, results do not depend on scheduling.
+__device__ __forceinline__ void row_stats(const float* __restrict__ st, int np, int row, float inv_d, float eps,
+                                          float& r, float& rmu) {
+    float s1 = 0.f, s2 = 0.f;
+    const float2* ps = reinterpret_cast<const float2*>(st) + (size_t)row * np;
+    for (int i = 0; i < np; ++i) {
+        const float2 v = __ldg(ps + i);
+        s1 += v.x;
+        s2 += v.y;
+    }
+    const float mu = s1 * inv_d;
+    r = rsqrtf(fmaxf(s2 * inv_d - mu * mu, 0.f) + eps);
+    rmu = r * mu;
+}
+__device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+
+// One 32-column unit in a fused mode. Mode 1: (ra, rb) = (1/std, mean/std) of this thread's row of the input.
+// Modes 2, 3: y = acc + bias + residual, (s1, s2) += (y, y^2); in mode 3 the residual is the LayerNorm of the row of
+// `resid` with (ra, rb) = (1/std, mean/std) of that row and gamma_s / beta_s.
+// This thread's 32 residual values of a unit (64 bytes of its row) as two 32-byte loads; zeros outside the tensor.
+__device__ __forceinline__ void resid_load(uint32_t (&r)[16], const half* __restrict__ resid, int N, int col0, int row, bool row_ok) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        if (row_ok && col0 + 16 * hh < N) {
+            const half* src = resid + (size_t)row * N + col0 + 16 * hh;
+            asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(r[8 * hh]), "=r"(r[8 * hh + 1]), "=r"(r[8 * hh + 2]), "=r"(r[8 * hh + 3]), "=r"(r[8 * hh + 4]),
+                           "=r"(r[8 * hh + 5]), "=r"(r[8 * hh + 6]), "=r"(r[8 * hh + 7])
+                         : "l"(src));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) r[8 * hh + i] = 0u;
+        }
+    }
+}
+
+template <bool kGelu, int kMode>
+__device__ __forceinline__ void epi_fused(const uint32_t (&acc)[32], const uint32_t (&rsd)[16], const GemmFusion& f, int N, int col0,
+                                          float ra, float rb, float& s1, float& s2, uint4 (&ov)[4]) {
+    half2* oh = reinterpret_cast<half2*>(ov);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {      // eight columns at a time
+        const int col = col0 + 8 * c;
+        float v[8];
+        if (col < N) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(acc[8 * c + i]);
+            if constexpr (kMode == 1) {
+                const float4 c0 = ldg4(f.colc + col), c1 = ldg4(f.colc + col + 4), d0 = ldg4(f.cold + col), d1 = ldg4(f.cold + col + 4);
+                const float cc[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                const float dd[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = fmaf(ra, v[i], fmaf(-rb, cc[i], dd[i]));
+            } else {
+                const float4 b0 = ldg4(f.bias_f32 + col), b1 = ldg4(f.bias_f32 + col + 4);
+                const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+                const half2* h2 = reinterpret_cast<const half2*>(&rsd[4 * c]);
+                float res[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 t = __half22float2(h2[i]);
+                    res[2 * i] = t.x;
+                    res[2 * i + 1] = t.y;
+                }
+                if constexpr (kMode == 3) {
+                    const float4 g0 = ldg4(f.gamma_s + col), g1 = ldg4(f.gamma_s + col + 4), e0 = ldg4(f.beta_s + col), e1 = ldg4(f.beta_s + col + 4);
+                    const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                    const float ee[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) res[i] = fmaf(fmaf(res[i], ra, -rb), gg[i], ee[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    v[i] += bb[i] + res[i];
+                    s1 += v[i];
+                    s2 = fmaf(v[i], v[i], s2);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const half2 hp = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+            oh[4 * c + i] = kGelu ? gelu_tanh_h2(hp) : hp;
+        }
+    }
+}
+
 // Persistent: CTA c processes tiles c, c + gridDim.x, ... (tile = slab * n_chunks + chunk, so CTAs that run
 // together share activations in L2). One chunk counter runs on across tiles and indexes two rings:
 //   * `stages` shared-memory stages (32 KB of activations + the weight block), free when the chunk's UMMAs
@@ -181,7 +279,7 @@ __device__ __forceinline__ void epi_write(uint8_t* buf, int lane, const uint4 (&
 // such chain (a version with a separate, earlier-freed activation ring needed a second wait per chunk in the
 // producer and a second commit in the movers and was 20-50 % slower).
 // While the issuer warps convert and store one tile, the producer and the movers stage the next tile's chunks.
-template <bool kGelu>
+template <bool kGelu, int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ GemmParams p) {
@@ -420,7 +518,61 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 const int units = (p.nb + 1) >> 1;
                 const bool more = tl + 1 < my_tiles;
                 const int col0 = chunk * p.nb * 16, row0 = slab * kSlab + q * 32;
-                for (int u = h; u < units && ok; u += ustep) {
+                if constexpr (kMode != 0) {
+                    // fused modes: one unit at a time, this thread's row statistics once per tile
+                    const int row = row0 + lane;
+                    const bool row_ok = row < p.T;
+                    float ra = 0.f, rb = 0.f, s1 = 0.f, s2 = 0.f;
+                    if (ok && row_ok) {
+                        if constexpr (kMode == 1) row_stats(p.fz.stats_in, p.fz.np_in, row, p.fz.inv_d_in, p.fz.eps, ra, rb);
+                        if constexpr (kMode == 3) row_stats(p.fz.stats_src, p.fz.np_src, row, p.fz.inv_d_src, p.fz.eps, ra, rb);
+                    }
+                    // the residual of a unit is requested one unit ahead (64 bytes per thread straight from global
+                    // memory: the row-per-thread pattern touches whole 32-byte sectors)
+                    uint32_t rnext[16];
+                    if constexpr (kMode >= 2) {
+                        if (ok && h < units) resid_load(rnext, p.fz.resid, p.N, col0 + h * kUnitCols, row, row_ok);
+                    }
+                    int it = 0;
+                    for (int u = h; u < units && ok; u += 2, ++it) {
+                        const bool two = u * 2 + 1 < p.nb;
+                        uint8_t* const buf = (p.epi_bufs == 2 && (it & 1)) ? buf1 : buf0;
+                        uint32_t acc[32];
+                        epi_load(tmem + lane_base + u * 32, two, acc);
+                        uint32_t rcur[16];
+                        if constexpr (kMode >= 2) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) rcur[i] = rnext[i];
+                            if (u + 2 < units) resid_load(rnext, p.fz.resid, p.N, col0 + (u + 2) * kUnitCols, row, row_ok);
+                        }
+                        tmem_ld_wait();
+                        if (more) {
+                            tmem_st16_zero(tmem + lane_base + u * 32);
+                            if (two) tmem_st16_zero(tmem + lane_base + u * 32 + 16);
+                        }
+                        uint4 ov[4];
+                        epi_fused<kGelu, kMode>(acc, rcur, p.fz, p.N, col0 + u * kUnitCols, ra, rb, s1, s2, ov);
+                        // the store that used this buffer has finished reading it (lane 0 issued them all)
+                        if (lane == 0) {
+                            if (p.epi_bufs == 2) tma_store_wait_read1();
+                            else tma_store_wait_read();
+                        }
+                        __syncwarp();
+                        epi_write(buf, lane, ov);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (col0 + u * kUnitCols < p.N) tma_store_2d(&tmY, buf, col0 + u * kUnitCols, row0);
+                            tma_store_commit();
+                        }
+                    }
+                    if constexpr (kMode >= 2) {
+                        // this warp's share of the row: its own slot, written whether or not the warp had a unit
+                        if (ok && row_ok)
+                            reinterpret_cast<float2*>(p.fz.stats_out)[(size_t)row * p.fz.np_out + chunk * 2 + h] = make_float2(s1, s2);
+                    }
+                }
+                for (int u = h; u < units && ok && kMode == 0; u += ustep) {
                     const int u2 = u + 2;
                     const bool second = p.epi_bufs == 2 && u2 < units;
                     const bool two_a = u * 2 + 1 < p.nb, two_b = u2 * 2 + 1 < p.nb;
@@ -485,6 +637,8 @@ struct TileWeight {
     uint2* d_dir = nullptr;
     uint8_t* d_stream = nullptr;
     half* d_bias = nullptr;
+    float* d_bias_f32 = nullptr;                 // the bias as fp32 (fused epilogues)
+    float* d_colc = nullptr; float* d_cold = nullptr;   // c_n, d_n of a weight folded with a LayerNorm's gamma / beta
     int* d_err = nullptr;
     size_t stream_bytes = 0;
 };
@@ -632,7 +786,13 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     cudaError_t e2 = cudaMalloc(&w->d_stream, std::max<size_t>(stream.size(), 16));
     cudaError_t e3 = cudaMalloc(&w->d_bias, (size_t)N * sizeof(half));
     cudaError_t e4 = cudaMalloc(&w->d_err, sizeof(int));
-    if (e1 || e2 || e3 || e4) { tile_weight_free(w); return fail(ET_ERR_CUDA, "tile weight: cudaMalloc failed"); }
+    cudaError_t e5 = cudaMalloc(&w->d_bias_f32, (size_t)N * sizeof(float));
+    if (e1 || e2 || e3 || e4 || e5) { tile_weight_free(w); return fail(ET_ERR_CUDA, "tile weight: cudaMalloc failed"); }
+    {
+        std::vector<float> bf((size_t)N, 0.f);
+        if (bias) for (int i = 0; i < N; ++i) bf[i] = __half2float(bias[i]);
+        cudaMemcpy(w->d_bias_f32, bf.data(), (size_t)N * sizeof(float), cudaMemcpyHostToDevice);
+    }
     cudaMemcpy(w->d_dir, dir.data(), dir.size() * sizeof(uint2), cudaMemcpyHostToDevice);
     cudaMemcpy(w->d_stream, stream.data(), stream.size(), cudaMemcpyHostToDevice);
     if (bias) cudaMemcpy(w->d_bias, bias, (size_t)N * sizeof(half), cudaMemcpyHostToDevice);
@@ -667,13 +827,15 @@ int tile_weight_concat(TileWeight** out, const TileWeight* const* parts, int cou
 void tile_weight_free(TileWeight* w) {
     if (!w) return;
     cudaFree(w->d_dir); cudaFree(w->d_stream); cudaFree(w->d_bias); cudaFree(w->d_err);
+    cudaFree(w->d_bias_f32); cudaFree(w->d_colc); cudaFree(w->d_cold);
     delete w;
 }
 
 static long long* g_prof = nullptr;
 void tile_gemm_set_profile_buffer(long long* dev_buf) { g_prof = dev_buf; }
 
-int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st, const half* bias_dev) {
+int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu, cudaStream_t st, const half* bias_dev,
+                    const GemmFusion* fusion) {
     if (!w || !Y || !X) return fail(ET_ERR_INVALID, "tile linear: null pointer");
     if (T < 0) return fail(ET_ERR_INVALID, "tile linear: negative token count");
     if (T == 0) return ET_OK;
@@ -682,11 +844,18 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     if (!make_tmap_panels_f16(&tm, X, (uint64_t)T, (uint64_t)w->K, (uint64_t)w->K, kSlab, kKC / kPanel) ||
         !make_tmap_2d_f16(&tmy, Y, (uint64_t)T, (uint64_t)w->N, (uint64_t)w->N, 32, kUnitCols, 64))
         return fail(ET_ERR_CUDA, "tile linear: cuTensorMapEncodeTiled failed");
+    using KernelFn = void (*)(CUtensorMap, CUtensorMap, GemmParams);
+    // [mode][gelu]; GELU exists for the plain and the normalised-input epilogues
+    static const KernelFn kernels[4][2] = {{tile_gemm_kernel<false, 0>, tile_gemm_kernel<true, 0>},
+                                           {tile_gemm_kernel<false, 1>, tile_gemm_kernel<true, 1>},
+                                           {tile_gemm_kernel<false, 2>, nullptr},
+                                           {tile_gemm_kernel<false, 3>, nullptr}};
     static PerDeviceOnce once;
     const cudaError_t attr_err = once.run([] {
-        cudaError_t e = cudaFuncSetAttribute(tile_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(tile_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
+        cudaError_t e = cudaSuccess;
+        for (int m = 0; m < 4 && e == cudaSuccess; ++m)
+            for (int g = 0; g < 2 && e == cudaSuccess; ++g)
+                if (kernels[m][g]) e = cudaFuncSetAttribute(kernels[m][g], cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemMax);
         return e;
     });
     if (attr_err != cudaSuccess) return cuda_status(attr_err, "tile linear: shared memory opt-in");
@@ -703,13 +872,71 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     // Packed for SM time (several batches in flight): a CTA takes several tiles in a row even when SMs are free,
     // so that set-up and pipeline fill are paid once and the next tile's loads run under an epilogue.
     dim3 grid(std::min((p.n_tiles + w->tiles_per_cta - 1) / w->tiles_per_cta, sm_count()));
-    const cudaError_t le = gelu ? launch_pdl(tile_gemm_kernel<true>, grid, dim3(kThreads), smem, st, tm, tmy, p)
-                                : launch_pdl(tile_gemm_kernel<false>, grid, dim3(kThreads), smem, st, tm, tmy, p);
+    const int mode = fusion ? fusion->mode : 0;
+    if (mode < 0 || mode > 3 || !kernels[mode][gelu ? 1 : 0]) return fail(ET_ERR_INVALID, "tile linear: no kernel for this epilogue");
+    if (mode) {
+        p.fz = *fusion;
+        p.fz.bias_f32 = w->d_bias_f32;
+        if (mode == 1) {
+            if (!w->d_colc || !w->d_cold || !p.fz.stats_in || p.fz.np_in <= 0) return fail(ET_ERR_INVALID, "tile linear: weight not folded for a normalised input");
+            p.fz.colc = w->d_colc;
+            p.fz.cold = w->d_cold;
+            p.fz.inv_d_in = 1.0f / (float)w->K;
+        } else {
+            if (!p.fz.resid || !p.fz.stats_out || p.fz.np_out != 2 * w->n_chunks) return fail(ET_ERR_INVALID, "tile linear: residual epilogue needs a residual and 2 x chunks partial slots");
+            if (mode == 3 && (!p.fz.stats_src || p.fz.np_src <= 0 || !p.fz.gamma_s || !p.fz.beta_s)) return fail(ET_ERR_INVALID, "tile linear: lazy residual needs its statistics and LayerNorm vectors");
+            p.fz.inv_d_src = 1.0f / (float)w->N;
+        }
+    } else {
+        p.fz = GemmFusion{};
+    }
+    const cudaError_t le = launch_pdl(kernels[mode][gelu ? 1 : 0], grid, dim3(kThreads), smem, st, tm, tmy, p);
     if (le != cudaSuccess) return cuda_status(le, "tile linear launch");
     return cuda_status(cudaGetLastError(), "tile linear launch");
 }
 
 int tile_weight_out_feat(const TileWeight* w) { return w->N; }
+int tile_weight_chunks(const TileWeight* w) { return w->n_chunks; }
+
+// The weight with a LayerNorm folded in: tile values multiplied by gamma of their input feature (rounded to fp16
+// again), c_n summed over those rounded values so that the epilogue's correction matches the products exactly.
+int tile_weight_fold(TileWeight** out, const TileWeight* w, const half* gamma, const half* beta) {
+    if (!out || !w || !gamma || !beta) return fail(ET_ERR_INVALID, "tile weight fold: null pointer");
+    *out = nullptr;
+    const int NBR = w->N / 16;
+    std::vector<half> data(w->h_data.size());
+    std::vector<double> c((size_t)w->N, 0.0), d((size_t)w->N, 0.0);
+    for (int r = 0; r < NBR; ++r)
+        for (int i = w->h_row_ptr[r]; i < w->h_row_ptr[r + 1]; ++i) {
+            const int k0 = w->h_row_offset[i];
+            for (int n = 0; n < 16; ++n)
+                for (int k = 0; k < 16; ++k) {
+                    const size_t at = (size_t)i * 256 + n * 16 + k;
+                    const float wv = __half2float(w->h_data[at]);
+                    const half folded = __float2half(wv * __half2float(gamma[k0 + k]));
+                    data[at] = folded;
+                    c[16 * r + n] += (double)__half2float(folded);
+                    d[16 * r + n] += (double)wv * (double)__half2float(beta[k0 + k]);
+                }
+        }
+    TileWeight* f = nullptr;
+    int rc = tile_weight_pack(&f, w->K, w->N, w->size_hint, w->ntile, data.data(), w->h_row_ptr.data(), w->h_row_offset.data(),
+                              w->h_bias.data(), 0);
+    if (rc) return rc;
+    std::vector<float> cf((size_t)w->N), df((size_t)w->N);
+    for (int n = 0; n < w->N; ++n) {
+        cf[n] = (float)c[n];
+        df[n] = (float)(d[n] + (double)__half2float(w->h_bias[n]));
+    }
+    if (cudaMalloc(&f->d_colc, cf.size() * sizeof(float)) != cudaSuccess || cudaMalloc(&f->d_cold, df.size() * sizeof(float)) != cudaSuccess) {
+        tile_weight_free(f);
+        return fail(ET_ERR_CUDA, "tile weight fold: cudaMalloc failed");
+    }
+    cudaMemcpy(f->d_colc, cf.data(), cf.size() * sizeof(float), cudaMemcpyHostToDevice);
+    cudaMemcpy(f->d_cold, df.data(), df.size() * sizeof(float), cudaMemcpyHostToDevice);
+    *out = f;
+    return ET_OK;
+}
 
 int tile_weight_error(const TileWeight* w, int* code) {
     int v = 0;

@@ -318,6 +318,13 @@ class Model:
                                        stream_ptr(stream)))
         return out
 
+    def set_layernorm_fusion(self, on):
+        check(lib().et_model_set_layernorm_fusion(self._h, _i(1 if on else 0)))
+
+    @property
+    def layernorm_fused(self):
+        return bool(lib().et_model_layernorm_fused(self._h))
+
     def check(self):
         """Raises EtError (ET_ERR_DEVICE_TIMEOUT) if a device-side wait of one of the stack's kernels gave up."""
         code = _i(0)

@@ -244,6 +244,16 @@ int et_model_reserve(et_model* model, int total_tokens, int batch, int max_len);
 int et_model_run_batch(et_model* model, void* out, const void* in, const int* seq_lens_host,
                        const int* valid_lens_host, int batch, void* stream);
 int et_model_set_graph_replay(et_model* model, int on);
+/* Optional form of a stack of tile / length layers: the residual-add + LayerNorm steps (encoder/encoder.cu:36-44)
+ * folded into the neighbouring linears, 5 launches per layer instead of 7 (the output projection and FFN2 add the
+ * residual and leave per-row sums, the next linear normalises in its epilogue with gamma folded into its weights,
+ * one plain LayerNorm ends the stack). OFF by default: on B200 the longer epilogues cost more than the two
+ * bandwidth-bound LayerNorm passes they replace (measured: 86 ms against 75 ms per step of the 24-layer BERT-large
+ * workload). Results differ from the default form by fp16 rounding of different intermediates, within the library's
+ * tolerance. on = 1 builds the folded weights (host work, synchronises); stacks with a row-pruned layer stay
+ * unfused; et_model_layernorm_fused tells which form is active. */
+int et_model_set_layernorm_fusion(et_model* model, int on);
+int et_model_layernorm_fused(const et_model* model);
 /* et_encoder_check over every layer of the stack (encoder/utils.h:4-12 is the reference's error path). */
 int et_model_check(et_model* model, int* code);
 

@@ -38,9 +38,9 @@ def test_model_equals_layers_one_by_one_and_oracle(et, orc):
         enc.run_batch(step, cur, lens, scratch)
         cur = step.clone()
     torch.cuda.synchronize()
-    # the stack: direct run, captured run, replayed run must all agree bit for bit with the chain
+    # the stack with separate LayerNorms: direct run, captured run, replayed run must all agree bit for bit with the chain
     model = et.Model([build_encoder(et, et.KIND_TILE, lin, ln, d, 128, H, T) for lin, ln in layers])
-    assert model.num_layers == n_layers
+    assert model.num_layers == n_layers and not model.layernorm_fused
     out = torch.zeros_like(x)
     for call in range(4):
         out.zero_()
@@ -48,6 +48,19 @@ def test_model_equals_layers_one_by_one_and_oracle(et, orc):
         torch.cuda.synchronize()
         assert torch.equal(out, cur), f"call {call}"
     util.assert_close(host(out), want.astype(np.float32), max_abs=4e-2, mean_abs=4e-3, what="3-layer stack vs oracle")
+    # the optional form, LayerNorms folded into the linears: same oracle, same tolerance, calls identical to each other
+    model.set_layernorm_fusion(True)
+    assert model.layernorm_fused
+    first = None
+    for call in range(4):
+        out.fill_(float("nan"))
+        model.run_batch(out, x, lens)
+        torch.cuda.synchronize()
+        util.assert_close(host(out), want.astype(np.float32), max_abs=4e-2, mean_abs=4e-3, what=f"3-layer stack, folded LayerNorms, call {call}")
+        first = out.clone() if first is None else first
+        assert torch.equal(out, first), f"folded LayerNorms, call {call}"
+    model.check()
+    model.set_layernorm_fusion(False)
     # in place, equal lengths, no graphs
     model.set_graph_replay(False)
     xe = dev(util.activations(32, (3 * 64, d)))
@@ -56,6 +69,46 @@ def test_model_equals_layers_one_by_one_and_oracle(et, orc):
     model.run_batch(xe, xe, [64] * 3)
     torch.cuda.synchronize()
     assert torch.equal(xe, ref)
+
+
+@pytest.mark.parametrize("kind_name", ["tile", "length"])
+def test_model_folded_layernorms_with_unit_scale_weights(et, orc, kind_name):
+    """Three layers with weights scaled so that every branch is as large as the residual, LayerNorm gamma and beta away
+    from 1 and 0, ragged lengths: the folded form (gamma multiplied into the next linear's weights, mean and 1/std
+    applied in its epilogue, the residual recomputed from the un-normalised tensor) against the oracle's chain, and
+    against the same stack with separate LayerNorms."""
+    d, H, dff, n_layers = 256, 4, 1024, 3
+    lens = [128, 37, 90, 5]
+    T = sum(lens)
+    kind = et.KIND_TILE if kind_name == "tile" else et.KIND_LENGTH
+    layers = [make_layer(orc, d, dff, 0.5, seed=90 + 7 * i, unit_scale=True) for i in range(n_layers)]
+    X = util.activations(91, (T, d))
+    want = X
+    for lin, ln in layers:
+        want = orc.encoder_layer(np.asarray(want, dtype=np.float16), orc_lin(lin), ln, lens, d, H).astype(np.float16)
+    x = dev(X)
+    model = et.Model([build_encoder(et, kind, lin, ln, d, 128, H, T) for lin, ln in layers])
+    model.set_layernorm_fusion(True)
+    assert model.layernorm_fused
+    out = torch.zeros_like(x)
+    for call in range(3):
+        out.fill_(float("nan"))
+        model.run_batch(out, x, lens)
+        torch.cuda.synchronize()
+        util.assert_close(host(out), want.astype(np.float32), max_abs=6e-2, mean_abs=6e-3, what=f"folded LayerNorms, unit scale, call {call}")
+    model.check()
+    plain = torch.zeros_like(x)
+    model.set_layernorm_fusion(False)
+    model.run_batch(plain, x, lens)
+    torch.cuda.synchronize()
+    util.assert_close(host(plain), want.astype(np.float32), max_abs=6e-2, mean_abs=6e-3, what="separate LayerNorms, unit scale")
+    util.assert_close(host(out), host(plain), max_abs=4e-2, mean_abs=4e-3, what="folded against separate LayerNorms")
+    # in place (out aliases in)
+    model.set_layernorm_fusion(True)
+    xi = x.clone()
+    model.run_batch(xi, xi, lens)
+    torch.cuda.synchronize()
+    assert torch.equal(xi, out)
 
 
 def test_model_alternating_batch_sizes(et, orc):
