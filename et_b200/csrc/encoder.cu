@@ -412,8 +412,8 @@ static int model_prepare_fusion(Model* m) {
             if (cudaMalloc(&f.lnf[i], v.size() * sizeof(float)) != cudaSuccess) { m->drop_fused(); return fail(ET_ERR_CUDA, "model: cudaMalloc failed"); }
             cudaMemcpy(f.lnf[i], v.data(), v.size() * sizeof(float), cudaMemcpyHostToDevice);
         }
-        f.np1 = 2 * tile_weight_chunks(e->lin[3]);
-        f.np2 = 2 * tile_weight_chunks(e->lin[5]);
+        f.np1 = tile_weight_stat_slots(e->lin[3]);
+        f.np2 = tile_weight_stat_slots(e->lin[5]);
     }
     m->fuse_ln = true;
     return ET_OK;

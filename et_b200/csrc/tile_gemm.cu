@@ -47,10 +47,14 @@ constexpr int kSlices = kKC / 16;   // UMMA K steps per chunk
 constexpr int kMaxNB = 24;          // block-rows per CTA (384 accumulator columns)
 constexpr int kSlotCols = kKC / 2;  // TMEM columns of one A slot
 constexpr int kMaxRing = 6;           // barriers per ring
-constexpr int kIssuers = 8;         // UMMA-issuing warps
+constexpr int kIssuers = 8;         // UMMA-issuing warps; they also take a share of every epilogue
+constexpr int kHelpers = 8;         // warps that only work in the epilogue (asleep on a hardware barrier otherwise)
 constexpr int kMovers = 2;          // tcgen05.cp-issuing warps, taking chunks in turn
 constexpr int kFirstIssuer = 1 + kMovers;
-constexpr int kThreads = 32 * (1 + kMovers + kIssuers);
+constexpr int kFirstHelper = kFirstIssuer + kIssuers;
+constexpr int kEpiWarps = kIssuers + kHelpers;
+constexpr int kEpiPerQuarter = kEpiWarps / 4;   // warps that share the 32 rows of a tensor-memory lane quarter
+constexpr int kThreads = 32 * (kFirstHelper + kHelpers);
 constexpr int kDirInParams = 32;    // directory entries of each chunk's first block travel as kernel parameters
 constexpr int kUnitCols = 32;          // columns per epilogue store
 constexpr int kUnitBytes = 32 * kUnitCols * 2;   // one warp's staging buffer: 32 rows x 32 columns
@@ -65,7 +69,7 @@ struct GemmParams {
     const uint8_t* stream;   // packed blocks
     half* Y;
     const half* bias;
-    int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, stages, a_slots, epi_bufs, gelu;
+    int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, stages, a_slots, gelu;
     int* err;
     uint2 first[kDirInParams];   // dir[chunk][0] for chunk < kDirInParams: no global load before the first TMA
     GemmFusion fz;           // LayerNorm folded into the epilogue (modes 1-3 of the kernel template)
@@ -110,7 +114,7 @@ __device__ __forceinline__ half2 gelu_tanh_h2(half2 x) {
 }
 
 struct Shared {
-    uint64_t full[kMaxRing];      // [chunk % stages]  the chunk's activations and weight block have landed (TMA)
+    uint64_t full[kMaxRing];      // [chunk % FB, FB even]  the chunk's activations and weight block have landed (TMA)
     uint64_t done[kMaxRing];      // [chunk % stages]  every issuer's UMMAs on the chunk have completed (8 commits)
     uint64_t a_ready[kMaxRing];   // [chunk % a_slots] the chunk's activations are in tensor memory (mover commit)
     uint64_t acc_done;            // 8 issuer commits after a tile's last chunk
@@ -286,11 +290,17 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int DB = p.stages, RA = p.a_slots;
+    // The `full` barriers form a ring of even length (the stages, twice over when their number is odd): a parity wait
+    // is only safe for a waiter that has seen the barrier's previous phase complete, and the two movers take chunks
+    // in turn, so every barrier must always fall to the same mover. (With three barriers for three stages a mover
+    // that found chunk c+1 landed before chunk c went on to chunk c+3, read the stale parity of the barrier that
+    // chunk c had yet to complete, and copied the slot early.)
+    const int FB = (DB & 1) ? 2 * DB : DB;
     const int slot_bytes = kXStageBytes + p.stage_b_bytes;   // multiple of 1024: activations, then the weight block
     uint8_t* const xbase = smem;
     uint8_t* const bbase = smem + kXStageBytes;
-    uint8_t* const epi = smem + (size_t)DB * slot_bytes;               // 8 warps x epi_bufs x 2 KB
-    Shared* sh = reinterpret_cast<Shared*>(epi + p.epi_bufs * kIssuers * kUnitBytes);
+    uint8_t* const epi = smem + (size_t)DB * slot_bytes;               // 16 warps x 2 KB
+    Shared* sh = reinterpret_cast<Shared*>(epi + kEpiWarps * kUnitBytes);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x;
     const uint32_t a_col0 = 512u - (uint32_t)(RA * kSlotCols);
@@ -319,7 +329,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         // Everything above touched only this kernel's own resources. The activations may still be in the making:
         // wait for the preceding kernels before the first copy (lane 0 issues them all).
         if (lane == 0) pdl_wait();
-        int issued = 0, bs = 0;
+        int issued = 0, bs = 0, fb = 0;
         uint32_t phb = 0;
         bool alive = true;
         for (int tl = 0; tl < my_tiles && alive; ++tl) {
@@ -347,20 +357,21 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 }
                 if (lane == 0) {
                     const uint32_t bbytes = d.y * 16u;
-                    mbar_expect_tx(&sh->full[bs], kXStageBytes + bbytes);
+                    mbar_expect_tx(&sh->full[fb], kXStageBytes + bbytes);
                     tma_load_3d(xbase + (size_t)bs * slot_bytes, &tmX, 0, slab * kSlab, kc * (kKC / kPanel),
-                                &sh->full[bs]);   // both panels, one op
-                    bulk_load(bbase + (size_t)bs * slot_bytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[bs]);
+                                &sh->full[fb]);   // both panels, one op
+                    bulk_load(bbase + (size_t)bs * slot_bytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[fb]);
                     if (issued < 64) ET_STAMP(100 + issued);
                 }
                 ++issued;
+                if (++fb == FB) fb = 0;
                 if (++bs == DB) { bs = 0; phb ^= 1u; }
             }
         }
         // Leaving early: wait (bounded) for the copies still in flight before the CTA exits.
         if (lane == 1 && sh->abort)
             for (int kk = issued > DB ? issued - DB : 0; kk < issued; ++kk)
-                mbar_wait(&sh->full[kk % DB], (uint32_t)(kk / DB) & 1u);
+                mbar_wait(&sh->full[kk % FB], (uint32_t)(kk / FB) & 1u);
     } else {
         if (warp == 1) {
             tmem_alloc(&sh->tmem_base, 512);
@@ -375,7 +386,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (warp >= kFirstIssuer) {
             const int w = warp - kFirstIssuer;
             const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-            for (int br = (w >> 2); br < p.nb; br += 2) tmem_st16_zero(tmem + lane_base + br * 16);
+            for (int br = (w >> 2); br < p.nb; br += kEpiPerQuarter) tmem_st16_zero(tmem + lane_base + br * 16);
             tmem_st_wait();
         }
         tc_fence_before();
@@ -389,13 +400,13 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             // chunks in turn (a warp needs ~1500 clocks per chunk: two barrier waits, eight tcgen05.cp, two
             // commits); lane 1 polls, lane 0 issues and commits.
             const int m = warp - 1;
-            int bs = m % DB, a = m % RA;
-            uint32_t phb = (uint32_t)(m / DB) & 1u;
+            int bs = m % DB, a = m % RA, fb = m;
+            uint32_t phf = 0;
             for (int it = m; it < n_items; it += kMovers) {
                 if (sh->abort) break;
                 int got = 1;
                 if (lane == 1) {
-                    got = mbar_wait(&sh->full[bs], phb);
+                    got = mbar_wait(&sh->full[fb], phf);
                     // the tensor-memory slot: the chunk a_slots before this one must be done
                     // (with as many slots as stages the producer has already waited for that chunk)
                     if (got && RA < DB && it >= RA) {
@@ -422,22 +433,25 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     if (it < 64) ET_STAMP(300 + it);
                 }
                 __syncwarp();
-                bs += kMovers;
-                while (bs >= DB) { bs -= DB; phb ^= 1u; }
+                bs = (bs + kMovers) % DB;
+                fb += kMovers;
+                if (fb >= FB) { fb -= FB; phf ^= 1u; }
                 a = (a + kMovers) % RA;
             }
         } else {
-            // ---------------- issuers: one UMMA per kept tile, A from tensor memory; then the tile's epilogue
-            const int w = warp - kFirstIssuer;
+            // ---------------- issuers (one UMMA per kept tile, A from tensor memory) and epilogue helpers. All sixteen
+            // warps share every tile's epilogue: its time is a chain of per-unit latencies in each warp (tensor-memory
+            // load, conversion, fence, TMA store issue: ~730 clocks per 32-column unit) while the tensor pipe idles,
+            // so four warps per lane quarter halve it; the stores themselves drain in the background.
+            const bool issuer = warp < kFirstHelper;
+            const int w = warp - kFirstIssuer;   // 0-7 issuers, 8-15 helpers
             const int q = warp & 3;   // the TMEM lane quarter this warp may read: rows 32q .. 32q + 31 of the slab
-            const int h = w >> 2;     // which of the two warps of this row quarter
+            const int h = w >> 2;     // which of the four warps of this row quarter
             const uint32_t lane_base = (uint32_t)(q * 32) << 16;
             // B tile descriptor: no swizzle, 128 B between core matrices along K, 256 B along N.
             const uint64_t b_desc0 = make_smem_desc(0, 128, 256, 0);
-            // this warp's output staging: 32 rows x 32 columns (64-byte rows, 64-byte swizzle), one or two buffers
-            uint8_t* const buf0 = epi + (size_t)w * p.epi_bufs * kUnitBytes;
-            uint8_t* const buf1 = buf0 + kUnitBytes;
-            const int ustep = 2 * p.epi_bufs;
+            // this warp's output staging: 32 rows x 32 columns (64-byte rows, 64-byte swizzle)
+            uint8_t* const buf = epi + (size_t)w * kUnitBytes;
             bool ok = true;
             int bs = 0, a = 0;
             uint32_t pha = 0;
@@ -447,60 +461,71 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 half* const tbias = sh->bias[tl & 1];
                 {
                     const int col0 = chunk * p.nb * 16;
-                    for (int i = tid - 32 * kFirstIssuer; i < p.nb * 16; i += 32 * kIssuers)
+                    for (int i = tid - 32 * kFirstIssuer; i < p.nb * 16; i += 32 * kEpiWarps)
                         tbias[i] = (col0 + i < p.N) ? p.bias[col0 + i] : __float2half(0.f);
                 }
                 // One rendezvous per tile: the bias is staged, every warp has cleared its accumulator columns,
                 // and a warp that gave up in the previous tile is seen by all.
-                named_barrier_sync(3, 32 * kIssuers);
+                named_barrier_sync(3, 32 * kEpiWarps);
                 if (tl > 0 && sh->issuer_abort[(tl - 1) & 1]) break;
                 tc_fence_after();
-                for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
+                if (issuer) {
+                    for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
+                        if (sh->abort) {
+                            sh->issuer_abort[tl & 1] = 1;
+                            ok = false;
+                            break;
+                        }
+                        // a_ready implies full: the movers waited for the chunk's TMA before copying. Lane 1 polls.
+                        int got = 1;
+                        if (lane == 1) {
+                            got = mbar_wait(&sh->a_ready[a], pha);
+                            if (w == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(500 + tl * p.k_chunks + kc);
+                        }
+                        got = __shfl_sync(0xffffffffu, got, 1);
+                        if (!got) {
+                            if (lane == 0) atomicExch(p.err, 13);
+                            sh->abort = 1;
+                            sh->issuer_abort[tl & 1] = 1;
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        const uint8_t* blk = bbase + (size_t)bs * slot_bytes;
+                        const uint32_t hw = reinterpret_cast<const uint32_t*>(blk)[w];
+                        const int e0 = hw & 0xffff, ne = hw >> 16;
+                        const uint32_t n_entries = reinterpret_cast<const uint32_t*>(blk)[8];
+                        const uint4* ent = reinterpret_cast<const uint4*>(blk + kHeaderBytes) + e0;
+                        const uint32_t tiles16 = (smem_u32(blk) + kHeaderBytes + n_entries * 16u) >> 4;
+                        const uint32_t abuf = tmem + a_col0 + a * kSlotCols;
+#pragma unroll 4
+                        for (int i = 0; i < ne; ++i) {
+                            const uint4 en = ent[i];
+                            if (elect_one())
+                                umma_f16_ts(tmem + en.z, abuf + en.y, b_desc0 | (uint64_t)((tiles16 + en.x) & 0x3fff), en.w, 1u);
+                        }
+                        if (elect_one()) umma_commit(&sh->done[bs]);
+                        if (w == 0 && lane == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(600 + tl * p.k_chunks + kc);
+                        __syncwarp();
+                        if (++bs == DB) bs = 0;
+                        if (++a == RA) { a = 0; pha ^= 1u; }
+                    }
+                    if (elect_one()) umma_commit(&sh->acc_done);
+                    __syncwarp();
+                    named_barrier_arrive(5, 32 * kEpiWarps);   // wakes the helpers: the tile's last UMMAs are on their way
+                } else {
+                    // asleep on a hardware barrier while the issuers run the main loop (polling warps would take issue
+                    // slots and shared-memory bandwidth from the warps on the critical path)
+                    named_barrier_sync(5, 32 * kEpiWarps);
                     if (sh->abort) {
                         sh->issuer_abort[tl & 1] = 1;
                         ok = false;
-                        break;
                     }
-                    // a_ready implies full: the movers waited for the chunk's TMA before copying. Lane 1 polls.
-                    int got = 1;
-                    if (lane == 1) {
-                        got = mbar_wait(&sh->a_ready[a], pha);
-                        if (w == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(500 + tl * p.k_chunks + kc);
-                    }
-                    got = __shfl_sync(0xffffffffu, got, 1);
-                    if (!got) {
-                        if (lane == 0) atomicExch(p.err, 13);
-                        sh->abort = 1;
-                        sh->issuer_abort[tl & 1] = 1;
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint8_t* blk = bbase + (size_t)bs * slot_bytes;
-                    const uint32_t hw = reinterpret_cast<const uint32_t*>(blk)[w];
-                    const int e0 = hw & 0xffff, ne = hw >> 16;
-                    const uint32_t n_entries = reinterpret_cast<const uint32_t*>(blk)[8];
-                    const uint4* ent = reinterpret_cast<const uint4*>(blk + kHeaderBytes) + e0;
-                    const uint32_t tiles16 = (smem_u32(blk) + kHeaderBytes + n_entries * 16u) >> 4;
-                    const uint32_t abuf = tmem + a_col0 + a * kSlotCols;
-#pragma unroll 4
-                    for (int i = 0; i < ne; ++i) {
-                        const uint4 e = ent[i];
-                        if (elect_one())
-                            umma_f16_ts(tmem + e.z, abuf + e.y, b_desc0 | (uint64_t)((tiles16 + e.x) & 0x3fff), e.w, 1u);
-                    }
-                    if (elect_one()) umma_commit(&sh->done[bs]);
-                    if (w == 0 && lane == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(600 + tl * p.k_chunks + kc);
-                    __syncwarp();
-                    if (++bs == DB) bs = 0;
-                    if (++a == RA) { a = 0; pha ^= 1u; }
                 }
-                if (elect_one()) umma_commit(&sh->acc_done);
-                __syncwarp();
 
-                // ---------------- epilogue, warp by warp with no rendezvous: the two warps of a row quarter take
-                // alternate 32-column units, two at a time where there are two staging buffers:
-                // TMEM -> registers -> bias / GELU -> fp16 -> the warp's own swizzled buffer -> TMA store.
+                // ---------------- epilogue, warp by warp with no rendezvous: the four warps of a row quarter take the
+                // tile's 32-column units in turn: TMEM -> registers -> bias / GELU (or a fused LayerNorm mode) -> fp16
+                // -> the warp's own swizzled buffer -> TMA store.
                 if (ok) {
                     int fin = 1;
                     if (lane == 1) fin = mbar_wait(&sh->acc_done, (uint32_t)tl & 1u);
@@ -518,92 +543,57 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 const int units = (p.nb + 1) >> 1;
                 const bool more = tl + 1 < my_tiles;
                 const int col0 = chunk * p.nb * 16, row0 = slab * kSlab + q * 32;
+                const int row = row0 + lane;
+                const bool row_ok = row < p.T;
+                float ra = 0.f, rb = 0.f, s1 = 0.f, s2 = 0.f;
                 if constexpr (kMode != 0) {
-                    // fused modes: one unit at a time, this thread's row statistics once per tile
-                    const int row = row0 + lane;
-                    const bool row_ok = row < p.T;
-                    float ra = 0.f, rb = 0.f, s1 = 0.f, s2 = 0.f;
+                    // fused modes: this thread's row statistics once per tile
                     if (ok && row_ok) {
                         if constexpr (kMode == 1) row_stats(p.fz.stats_in, p.fz.np_in, row, p.fz.inv_d_in, p.fz.eps, ra, rb);
                         if constexpr (kMode == 3) row_stats(p.fz.stats_src, p.fz.np_src, row, p.fz.inv_d_src, p.fz.eps, ra, rb);
                     }
-                    // the residual of a unit is requested one unit ahead (64 bytes per thread straight from global
-                    // memory: the row-per-thread pattern touches whole 32-byte sectors)
-                    uint32_t rnext[16];
-                    if constexpr (kMode >= 2) {
-                        if (ok && h < units) resid_load(rnext, p.fz.resid, p.N, col0 + h * kUnitCols, row, row_ok);
-                    }
-                    int it = 0;
-                    for (int u = h; u < units && ok; u += 2, ++it) {
-                        const bool two = u * 2 + 1 < p.nb;
-                        uint8_t* const buf = (p.epi_bufs == 2 && (it & 1)) ? buf1 : buf0;
-                        uint32_t acc[32];
-                        epi_load(tmem + lane_base + u * 32, two, acc);
-                        uint32_t rcur[16];
-                        if constexpr (kMode >= 2) {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) rcur[i] = rnext[i];
-                            if (u + 2 < units) resid_load(rnext, p.fz.resid, p.N, col0 + (u + 2) * kUnitCols, row, row_ok);
-                        }
-                        tmem_ld_wait();
-                        if (more) {
-                            tmem_st16_zero(tmem + lane_base + u * 32);
-                            if (two) tmem_st16_zero(tmem + lane_base + u * 32 + 16);
-                        }
-                        uint4 ov[4];
-                        epi_fused<kGelu, kMode>(acc, rcur, p.fz, p.N, col0 + u * kUnitCols, ra, rb, s1, s2, ov);
-                        // the store that used this buffer has finished reading it (lane 0 issued them all)
-                        if (lane == 0) {
-                            if (p.epi_bufs == 2) tma_store_wait_read1();
-                            else tma_store_wait_read();
-                        }
-                        __syncwarp();
-                        epi_write(buf, lane, ov);
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            if (col0 + u * kUnitCols < p.N) tma_store_2d(&tmY, buf, col0 + u * kUnitCols, row0);
-                            tma_store_commit();
-                        }
-                    }
-                    if constexpr (kMode >= 2) {
-                        // this warp's share of the row: its own slot, written whether or not the warp had a unit
-                        if (ok && row_ok)
-                            reinterpret_cast<float2*>(p.fz.stats_out)[(size_t)row * p.fz.np_out + chunk * 2 + h] = make_float2(s1, s2);
-                    }
                 }
-                for (int u = h; u < units && ok && kMode == 0; u += ustep) {
-                    const int u2 = u + 2;
-                    const bool second = p.epi_bufs == 2 && u2 < units;
-                    const bool two_a = u * 2 + 1 < p.nb, two_b = u2 * 2 + 1 < p.nb;
-                    uint32_t acc_a[32], acc_b[32];
-                    epi_load(tmem + lane_base + u * 32, two_a, acc_a);
-                    if (second) epi_load(tmem + lane_base + u2 * 32, two_b, acc_b);
+                // the residual of a unit is requested one unit ahead (64 bytes per thread straight from global
+                // memory: the row-per-thread pattern touches whole 32-byte sectors)
+                uint32_t rnext[16];
+                if constexpr (kMode >= 2) {
+                    if (ok && h < units) resid_load(rnext, p.fz.resid, p.N, col0 + h * kUnitCols, row, row_ok);
+                }
+                for (int u = h; u < units && ok; u += kEpiPerQuarter) {
+                    const bool two = u * 2 + 1 < p.nb;
+                    uint32_t acc[32];
+                    epi_load(tmem + lane_base + u * 32, two, acc);
+                    uint32_t rcur[16];
+                    if constexpr (kMode >= 2) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) rcur[i] = rnext[i];
+                        if (u + kEpiPerQuarter < units)
+                            resid_load(rnext, p.fz.resid, p.N, col0 + (u + kEpiPerQuarter) * kUnitCols, row, row_ok);
+                    }
                     tmem_ld_wait();
                     if (more) {   // clear what was just read, for the next tile
                         tmem_st16_zero(tmem + lane_base + u * 32);
-                        if (two_a) tmem_st16_zero(tmem + lane_base + u * 32 + 16);
-                        if (second) {
-                            tmem_st16_zero(tmem + lane_base + u2 * 32);
-                            if (two_b) tmem_st16_zero(tmem + lane_base + u2 * 32 + 16);
-                        }
+                        if (two) tmem_st16_zero(tmem + lane_base + u * 32 + 16);
                     }
-                    uint4 ov_a[4], ov_b[4];
-                    epi_convert<kGelu>(acc_a, tbias + u * 32, two_a, ov_a);
-                    if (second) epi_convert<kGelu>(acc_b, tbias + u2 * 32, two_b, ov_b);
-                    // the buffers' previous stores must have finished reading them (lane 0 issued them)
+                    uint4 ov[4];
+                    if constexpr (kMode == 0) epi_convert<kGelu>(acc, tbias + u * 32, two, ov);
+                    else epi_fused<kGelu, kMode>(acc, rcur, p.fz, p.N, col0 + u * kUnitCols, ra, rb, s1, s2, ov);
+                    // the buffer's previous store must have finished reading it (lane 0 issued it)
                     if (lane == 0) tma_store_wait_read();
                     __syncwarp();
-                    epi_write(buf0, lane, ov_a);
-                    if (second) epi_write(buf1, lane, ov_b);
+                    epi_write(buf, lane, ov);
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if (col0 + u * kUnitCols < p.N) tma_store_2d(&tmY, buf0, col0 + u * kUnitCols, row0);
-                        if (second && col0 + u2 * kUnitCols < p.N) tma_store_2d(&tmY, buf1, col0 + u2 * kUnitCols, row0);
+                        if (col0 + u * kUnitCols < p.N) tma_store_2d(&tmY, buf, col0 + u * kUnitCols, row0);
                         tma_store_commit();
                         if (w == 0 && tl < 16 && (u >> 2) < 14) ET_STAMP(1400 + tl * 16 + 1 + (u >> 2));
                     }
+                }
+                if constexpr (kMode >= 2) {
+                    // this warp's share of the row: its own slot, written whether or not the warp had a unit
+                    if (ok && row_ok)
+                        reinterpret_cast<float2*>(p.fz.stats_out)[(size_t)row * p.fz.np_out + chunk * kEpiPerQuarter + h] = make_float2(s1, s2);
                 }
                 if (more) {
                     tmem_st_wait();
@@ -626,7 +616,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 // --------------------------------------------------------------------------------- host side
 
 struct TileWeight {
-    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, stages = 0, a_slots = 0, epi_bufs = 1;
+    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, stages = 0, a_slots = 0;
     int tiles_per_cta = 1;   // > 1 when packed for SM time: a CTA takes that many tiles even when SMs are free
     long ntile = 0;
     int size_hint = 0;
@@ -647,15 +637,15 @@ struct TileWeight {
 // no longer what bounds the chunk period), with two epilogue staging buffers per warp when they do not cost a
 // stage. A stage goes round in ~4000 clocks (TMA, tcgen05.cp, UMMAs, and the polls between them), a
 // tensor-memory slot in ~2000.
-struct RingShape { int stages, a_slots, epi_bufs; double period; };
+struct RingShape { int stages, a_slots; double period; };
 static RingShape ring_shape(int nb, int stage_b_bytes) {
     const int tmem_slots = std::min(kMaxRing, (512 - nb * 16) / kSlotCols);
     const int slot = kXStageBytes + stage_b_bytes;
-    const int avail1 = kSmemMax - 1024 - (int)sizeof(Shared) - kIssuers * kUnitBytes;
-    const int cap = 4;
+    const int avail1 = kSmemMax - 1024 - (int)sizeof(Shared) - kEpiWarps * kUnitBytes;
+    const int cap = 4;   // an odd number of stages uses twice as many `full` barriers
+    static_assert(kMovers == 2 && 2 * 3 <= kMaxRing && cap <= kMaxRing, "the full-barrier ring must fit");
     RingShape r;
     r.stages = std::min(cap, avail1 / slot);
-    r.epi_bufs = (avail1 - r.stages * slot >= kIssuers * kUnitBytes) ? 2 : 1;
     r.a_slots = std::min(r.stages, tmem_slots);
     r.period = r.stages >= 1 && r.a_slots >= 1 ? std::max(4000.0 / r.stages, 2000.0 / r.a_slots) : 1e30;
     return r;
@@ -777,7 +767,7 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     w->stage_b_bytes = (int)((max_block + 1023) / 1024 * 1024);
     {
         const RingShape rs = ring_shape(w->nb, w->stage_b_bytes);
-        w->stages = rs.stages; w->a_slots = rs.a_slots; w->epi_bufs = rs.epi_bufs;
+        w->stages = rs.stages; w->a_slots = rs.a_slots;
     }
     if (w->stages < 2 || w->a_slots < 1) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
     w->stream_bytes = stream.size();
@@ -864,11 +854,11 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     p.T = T; p.N = w->N; p.k_chunks = w->k_chunks; p.nb = w->nb;
     p.n_chunks = w->n_chunks;
     p.n_tiles = ((T + kSlab - 1) / kSlab) * w->n_chunks;
-    p.stage_b_bytes = w->stage_b_bytes; p.stages = w->stages; p.a_slots = w->a_slots; p.epi_bufs = w->epi_bufs; p.gelu = gelu; p.err = w->d_err;
+    p.stage_b_bytes = w->stage_b_bytes; p.stages = w->stages; p.a_slots = w->a_slots; p.gelu = gelu; p.err = w->d_err;
     p.prof = g_prof;
     for (size_t c = 0; c < w->h_first.size(); ++c) p.first[c] = w->h_first[c];
     const size_t smem = (size_t)w->stages * (kXStageBytes + w->stage_b_bytes) +
-                        (size_t)w->epi_bufs * kIssuers * kUnitBytes + sizeof(Shared) + 1024;
+                        (size_t)kEpiWarps * kUnitBytes + sizeof(Shared) + 1024;
     // Packed for SM time (several batches in flight): a CTA takes several tiles in a row even when SMs are free,
     // so that set-up and pipeline fill are paid once and the next tile's loads run under an epilogue.
     dim3 grid(std::min((p.n_tiles + w->tiles_per_cta - 1) / w->tiles_per_cta, sm_count()));
@@ -883,7 +873,7 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
             p.fz.cold = w->d_cold;
             p.fz.inv_d_in = 1.0f / (float)w->K;
         } else {
-            if (!p.fz.resid || !p.fz.stats_out || p.fz.np_out != 2 * w->n_chunks) return fail(ET_ERR_INVALID, "tile linear: residual epilogue needs a residual and 2 x chunks partial slots");
+            if (!p.fz.resid || !p.fz.stats_out || p.fz.np_out != kEpiPerQuarter * w->n_chunks) return fail(ET_ERR_INVALID, "tile linear: residual epilogue needs a residual and 4 x chunks partial slots");
             if (mode == 3 && (!p.fz.stats_src || p.fz.np_src <= 0 || !p.fz.gamma_s || !p.fz.beta_s)) return fail(ET_ERR_INVALID, "tile linear: lazy residual needs its statistics and LayerNorm vectors");
             p.fz.inv_d_src = 1.0f / (float)w->N;
         }
@@ -897,6 +887,7 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
 
 int tile_weight_out_feat(const TileWeight* w) { return w->N; }
 int tile_weight_chunks(const TileWeight* w) { return w->n_chunks; }
+int tile_weight_stat_slots(const TileWeight* w) { return kEpiPerQuarter * w->n_chunks; }
 
 // The weight with a LayerNorm folded in: tile values multiplied by gamma of their input feature (rounded to fp16
 // again), c_n summed over those rounded values so that the epilogue's correction matches the products exactly.

@@ -12,7 +12,7 @@ struct TileWeight;
 //           producer's column chunks) give mean and 1/std, applied in the epilogue; the weight must have been folded
 //           with the LayerNorm's gamma / beta (tile_weight_fold).
 //   mode 2: Y = X W^T + bias + resid (resid fp16 [T x N]); per-row partial sums of Y to stats_out[T][np_out][2],
-//           np_out = 2 x the weight's column chunks.
+//           np_out = tile_weight_stat_slots(weight).
 //   mode 3: the same with resid = LayerNorm(row of `resid`) from stats_src / gamma_s / beta_s (fp32 [N]).
 struct GemmFusion {
     int mode = 0;
@@ -41,8 +41,9 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
 // New weight = w with gamma multiplied into its input features and the column vectors c_n = sum_k gamma_k W_nk,
 // d_n = sum_k beta_k W_nk + bias_n that the mode-1 epilogue needs (gamma, beta: host, in_feat values).
 int tile_weight_fold(TileWeight** out, const TileWeight* w, const half* gamma, const half* beta);
-// Column chunks of the packed weight (partial-sum slots per row = 2 x this).
+// Column chunks of the packed weight, and the partial-sum slots per row that its residual epilogue writes.
 int tile_weight_chunks(const TileWeight* w);
+int tile_weight_stat_slots(const TileWeight* w);
 // Reads and clears the device error word (0 = no bounded wait gave up). Synchronises.
 int tile_weight_error(const TileWeight* w, int* code);
 void tile_weight_info(const TileWeight* w, int* info6);
