@@ -144,35 +144,80 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
     if (tid == 0) AT_STAMP(0);
     pdl_launch_dependents();
 
-    if (tid == 0) {
-        mbar_init(&sh->q_full, 1);
-        for (int j = 0; j < 2; ++j) { mbar_init(&sh->k_full[j], 1); mbar_init(&sh->v_full[j], 1); }
-        mbar_init(&sh->s_ready, 1);
-        mbar_init(&sh->p_ready, 32 * kSoftmaxWarps);
-        mbar_init(&sh->pv_done, 1);
-        mbar_init(&sh->o_done, 1);
-        sh->abort = 0;
-        fence_mbar_init();
-    }
+    // The warp that issues the copies sets up the barriers, finds the CTA's work item and starts the first loads
+    // (Q, K_0, V_0, K_1, V_1) before anything CTA-wide happens: they are in flight during the tensor-memory
+    // allocation and the rendezvous. Q/K/V come from DRAM, and a wave's CTAs all start together.
     if (warp == kSoftmaxWarps) {
-        tmem_alloc(&sh->tmem_base, kTmemCols);
-        tmem_relinquish();
-    }
-    pdl_wait();   // lengths and activations come from the preceding kernels
-    if (tid == 32) {
-        int b = -1, tok0 = 0, q0 = 0, blk = blockIdx.x;
+        if (lane == 0) {
+            mbar_init(&sh->q_full, 1);
+            for (int j = 0; j < 2; ++j) { mbar_init(&sh->k_full[j], 1); mbar_init(&sh->v_full[j], 1); }
+            mbar_init(&sh->s_ready, 1);
+            mbar_init(&sh->p_ready, 32 * kSoftmaxWarps);
+            mbar_init(&sh->pv_done, 1);
+            mbar_init(&sh->o_done, 1);
+            sh->abort = 0;
+            fence_mbar_init();
+            prefetch_tmap(&tmQ);
+            prefetch_tmap(&tmK);
+            prefetch_tmap(&tmV);
+        }
+        pdl_wait();   // lengths and activations come from the preceding kernels
+        int b = -1, tok0 = 0, q0 = 0, len = 0;
         if (p.cu_seqlens) {
-            for (int i = 0; i < p.batch; ++i) {
-                const int L = p.cu_seqlens[i + 1] - p.cu_seqlens[i];
-                const int nb = (L + kBQ - 1) / kBQ;
-                if (blk < nb) { b = i; tok0 = p.cu_seqlens[i]; q0 = blk * kBQ; break; }
-                blk -= nb;
+            // 32 sequences per round: each lane takes one, a prefix sum of their query-block counts locates the block
+            int blk = blockIdx.x;
+            for (int base = 0; base < p.batch && b < 0; base += 32) {
+                const int i = base + lane;
+                const int t0 = i < p.batch ? p.cu_seqlens[i] : 0;
+                const int Li = i < p.batch ? p.cu_seqlens[i + 1] - t0 : 0;
+                const int nbi = (Li + kBQ - 1) / kBQ;
+                int incl = nbi;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                    if (lane >= o) incl += v;
+                }
+                const unsigned hit = __ballot_sync(0xffffffffu, blk < incl);
+                if (hit) {
+                    const int src = __ffs(hit) - 1;
+                    const int excl = __shfl_sync(0xffffffffu, incl - nbi, src);
+                    b = base + src;
+                    tok0 = __shfl_sync(0xffffffffu, t0, src);
+                    len = __shfl_sync(0xffffffffu, Li, src);
+                    q0 = (blk - excl) * kBQ;
+                } else {
+                    blk -= __shfl_sync(0xffffffffu, incl, 31);
+                }
             }
         } else {
             const int nb = (p.uniform_len + kBQ - 1) / kBQ;
-            if (blk < nb * p.batch) { b = blk / nb; tok0 = b * p.uniform_len; q0 = (blk % nb) * kBQ; }
+            const int blk = blockIdx.x;
+            if (blk < nb * p.batch) { b = blk / nb; tok0 = b * p.uniform_len; q0 = (blk % nb) * kBQ; len = p.uniform_len; }
         }
-        sh->seq[0] = b; sh->seq[1] = tok0; sh->seq[2] = q0;
+        int nvalid = 0;
+        if (b >= 0) nvalid = p.valid_lens ? min(p.valid_lens[b], len) : len;
+        if (lane == 0) {
+            sh->seq[0] = b; sh->seq[1] = tok0; sh->seq[2] = q0;
+            if (b >= 0 && nvalid > 0) {
+                mbar_expect_tx(&sh->q_full, kTile);
+                tma_load_2d(sQ, &tmQ, h * kHD, tok0 + q0, &sh->q_full);
+                mbar_expect_tx(&sh->k_full[0], kTile);
+                tma_load_2d(sK, &tmK, h * kHD, tok0, &sh->k_full[0]);
+                mbar_expect_tx(&sh->v_full[0], kTile);
+                tma_load_2d(sV, &tmV, h * kHD, tok0, &sh->v_full[0]);
+                if (nvalid > kBK) {
+                    mbar_expect_tx(&sh->k_full[1], kTile);
+                    tma_load_2d(sK + kTile, &tmK, h * kHD, tok0 + kBK, &sh->k_full[1]);
+                    mbar_expect_tx(&sh->v_full[1], kTile);
+                    tma_load_2d(sV + kTile, &tmV, h * kHD, tok0 + kBK, &sh->v_full[1]);
+                }
+            }
+        }
+        __syncwarp();
+        tmem_alloc(&sh->tmem_base, kTmemCols);
+        tmem_relinquish();
+    } else {
+        pdl_wait();
     }
     tc_fence_before();
     __syncthreads();
@@ -200,11 +245,7 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                     mbar_expect_tx(&sh->v_full[st], kTile);
                     tma_load_2d(sV + (size_t)st * kTile, &tmV, h * kHD, tok0 + j * kBK, &sh->v_full[st]);
                 };
-                mbar_expect_tx(&sh->q_full, kTile);
-                tma_load_2d(sQ, &tmQ, h * kHD, tok0 + q0, &sh->q_full);
-                load_k(0);
-                load_v(0);
-                if (nkb > 1) { load_k(1); load_v(1); }
+                // (Q and the first two K/V blocks were requested before the CTA-wide set-up)
                 const uint32_t idesc_qk = make_idesc_f16(128, 128);
                 const uint32_t idesc_pv = make_idesc_f16(128, 64, false, true);   // V is an MN-major B operand
                 const uint32_t qa = smem_u32(sQ);
