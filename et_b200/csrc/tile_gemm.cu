@@ -7,7 +7,7 @@
 //     Its fp32 accumulators live in tensor memory: 16 TMEM columns per block-row, 384 columns at most.
 //   * The activations are the A operand and are read from tensor memory, not shared memory: X is
 //     brought in by TMA (two 128-byte-swizzled 128 x 64 panels per 128-wide K chunk) and moved
-//     smem -> TMEM with tcgen05.cp into one of 2-6 64-column slots. With A in TMEM a 128x16x16 UMMA no
+//     smem -> TMEM with tcgen05.cp into one of 2-4 64-column slots. With A in TMEM a 128x16x16 UMMA no
 //     longer pays the 4 KB shared-memory read of A, which otherwise bounds small-N UMMAs to ~20 % of peak.
 //   * Every kept tile is one UMMA  D[128 x 16] += A[128 x 16] . tile^T  (B operand = the tile in
 //     shared memory, canonical no-swizzle K-major layout). A single warp can only issue one UMMA per
@@ -20,8 +20,9 @@
 //     role and chunk: producer waits done -> TMA; mover waits full -> tcgen05.cp -> commit a_ready; issuers wait
 //     a_ready -> UMMAs -> commit done. (Every asynchronous operation costs the issuing warp 100-250 clocks, so
 //     the hops per chunk are what the loop time is made of.)
-//   * Epilogue, warp by warp: tcgen05.ld, + bias, optional GELU, fp16, staged in the warp's own 64-byte-swizzled
-//     32 x 32 buffer and written with one TMA store (rows beyond T and columns beyond N are clipped).
+//   * Epilogue, warp by warp, by sixteen warps (the eight issuers and eight helpers that sleep on a hardware
+//     barrier during the main loop): tcgen05.ld, + bias, optional GELU, fp16, staged in the warp's own
+//     64-byte-swizzled 32 x 32 buffer and written with one TMA store (rows beyond T and columns beyond N are clipped).
 // Every mbarrier wait is bounded; a wait that gives up records a code in the error word, the CTA
 // stops issuing, frees its tensor memory and returns.
 #include <algorithm>
