@@ -3,20 +3,21 @@
 // et_attention_batch (the mma.sync kernel in attention.cu covers every other variant).
 // Replaces kernels/attention.cu:51-134 of the reference for that case.
 //
-// A CTA owns 128 queries of one head of one sequence, one TMEM lane per query:
-//   S_j = Q K_j^T      SS UMMA 128x128x16 (x4), Q and the 128-key block K_j in shared memory (TMA, 128-byte
-//                      swizzle), fp32 S_j in 128 TMEM columns
-//   softmax            eight warps, two threads per query row (64 keys each): tcgen05.ld, scale (log2 domain),
-//                      additive mask, key validity, running max / sum in fp32, P_j = 2^(s - max) as packed fp16
-//                      into 64 more TMEM columns (tcgen05.st), O rescaled by 2^(old max - new max) in place.
-//                      P has its own columns, so Q K_{j+1}^T is issued together with P_j V_j and the next
-//                      block's row maxima are computed while P_j V_j runs
-//   O += P_j V_j       TS UMMA 128x64x16 (x8): A = P_j read from tensor memory, B = V_j in shared memory as loaded
-//                      (rows = keys), used as an MN-major operand
+// A CTA owns 128 queries of one head of one sequence, one TMEM lane and one thread per query:
+//   S_j = Q K_j^T      SS UMMA 128x64x16 (x4), Q and the 64-key block K_j in shared memory (TMA, 128-byte
+//                      swizzle), fp32 S_j in 64 TMEM columns
+//   softmax            four warps, one thread per query row, one pass per block: tcgen05.ld of the row's 64 scores,
+//                      scale (log2 domain), additive mask, key validity, row maximum; if the maximum has grown by
+//                      more than 2^8 the reference point moves and O is rescaled in place; P_j = 2^(s - reference) as
+//                      packed fp16 over the first 32 score columns (tcgen05.st), row sum in fp32. No exchange
+//                      between threads, no second pass
+//   O += P_j V_j       TS UMMA 128x64x16 (x4): A = P_j read from tensor memory, B = V_j in shared memory as loaded
+//                      (rows = keys), used as an MN-major operand; Q K_{j+1}^T is issued right behind it into the
+//                      columns that hold P_j (tcgen05 operations execute in issue order)
 //   epilogue           O / row sum -> fp16 -> global, rows beyond the sequence are not written
-// The S x S matrix never leaves the SM. K_j / V_j stream through a two-stage ring, so a CTA needs 80 KB of
-// shared memory and 256 TMEM columns and two CTAs share an SM: one CTA's softmax runs under the other's
-// UMMAs and loads. Every mbarrier wait is bounded; a wait that gives up
+// The S x S matrix never leaves the SM. K_j / V_j stream through a two-stage ring. A CTA needs 48 KB of shared
+// memory, 128 TMEM columns and 160 threads, so four CTAs share an SM: while one CTA's softmax runs, the UMMAs,
+// loads and hand-overs of the other three are in flight. Every mbarrier wait is bounded; a wait that gives up
 // sets the error word and the CTA leaves through the common exit, freeing its tensor memory.
 #include <mutex>
 #include "attention.h"
@@ -28,12 +29,22 @@ namespace et {
 
 namespace {
 
-constexpr int kBQ = 128, kBK = 128, kHD = 64;
-constexpr int kTile = kBQ * kHD * 2;      // 16 KB: one 128 x 64 fp16 tile
-constexpr int kSoftmaxWarps = 8;          // two threads per query row, each owns 64 of the 128 keys of a block
+// Keys per block: 64 (four CTAs per SM) or 128 (two). Measured at 256 x 512 tokens, 16 heads: 731 us against 812 us;
+// with two threads per row and three CTAs per SM 801 us; the earlier two-pass form with 128 keys, two threads per row
+// and two CTAs per SM 767 us. Sixteen resident softmax warps with the shortest hand-overs between them win.
+#ifndef ET_ATTN_BK
+#define ET_ATTN_BK 64
+#endif
+constexpr int kBQ = 128, kBK = ET_ATTN_BK, kHD = 64;
+static_assert(kBK == 64 || kBK == 128, "key blocks of 64 or 128");
+constexpr int kNCh = kBK / 32;            // 32-column chunks of a score row
+constexpr int kTile = kBQ * kHD * 2;      // 16 KB: the 128 x 64 fp16 Q tile
+constexpr int kKVTile = kBK * kHD * 2;    // one key block of K or V
+constexpr int kSoftmaxWarps = 4;          // one thread per query row
 constexpr int kThreads = 32 * (kSoftmaxWarps + 1);   // + 1 warp whose lane 0 issues TMA and UMMA
-constexpr int kTmemCols = 256;            // S 128 | P 64 | O 64: two CTAs share an SM's tensor memory
-constexpr uint32_t kPCol = 128, kOCol = 192;
+constexpr int kCtasPerSm = kBK == 64 ? 4 : 2;
+constexpr int kTmemCols = kBK + 64 <= 128 ? 128 : 256;   // S (P overlays its first half) | O 64
+constexpr uint32_t kPCol = 0, kOCol = kBK;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.f;       // log2 units by which a row maximum must grow before O is rescaled
 
@@ -60,7 +71,6 @@ struct TcShared {
     uint32_t tmem_base;
     int seq[3];
     volatile int abort;
-    float xmax[2][kBQ];   // block maximum (at the end: sum) of each half-row, exchanged between the two threads of a row
 };
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -99,11 +109,6 @@ __device__ __forceinline__ float sum_packed(const uint32_t (&pk)[16]) {
     return s;
 }
 
-// The two warps that share a quarter of the rows (64 threads) meet on their own hardware barrier.
-__device__ __forceinline__ void named_pair_sync(int id) {
-    asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
-}
-
 // 32 additive mask values of one query row (keys k0..k0+31), times log2(e); zero where there is no mask row.
 __device__ __forceinline__ void load_mask32(float (&mk)[32], const half* mrow, int k0, int limit, bool vec) {
     if (!mrow) {
@@ -129,7 +134,7 @@ __device__ __forceinline__ void load_mask32(float (&mk)[32], const half* mrow, i
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                   const __grid_constant__ CUtensorMap tmK,
                                                                   const __grid_constant__ CUtensorMap tmV,
                                                                   const __grid_constant__ TcParams p) {
@@ -137,8 +142,8 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* sQ = smem;
     uint8_t* sK = smem + kTile;          // 2 stages
-    uint8_t* sV = sK + 2 * kTile;        // 2 stages
-    TcShared* sh = reinterpret_cast<TcShared*>(sV + 2 * kTile);
+    uint8_t* sV = sK + 2 * kKVTile;      // 2 stages
+    TcShared* sh = reinterpret_cast<TcShared*>(sV + 2 * kKVTile);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y;
     if (tid == 0) AT_STAMP(0);
@@ -201,15 +206,15 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
             if (b >= 0 && nvalid > 0) {
                 mbar_expect_tx(&sh->q_full, kTile);
                 tma_load_2d(sQ, &tmQ, h * kHD, tok0 + q0, &sh->q_full);
-                mbar_expect_tx(&sh->k_full[0], kTile);
+                mbar_expect_tx(&sh->k_full[0], kKVTile);
                 tma_load_2d(sK, &tmK, h * kHD, tok0, &sh->k_full[0]);
-                mbar_expect_tx(&sh->v_full[0], kTile);
+                mbar_expect_tx(&sh->v_full[0], kKVTile);
                 tma_load_2d(sV, &tmV, h * kHD, tok0, &sh->v_full[0]);
                 if (nvalid > kBK) {
-                    mbar_expect_tx(&sh->k_full[1], kTile);
-                    tma_load_2d(sK + kTile, &tmK, h * kHD, tok0 + kBK, &sh->k_full[1]);
-                    mbar_expect_tx(&sh->v_full[1], kTile);
-                    tma_load_2d(sV + kTile, &tmV, h * kHD, tok0 + kBK, &sh->v_full[1]);
+                    mbar_expect_tx(&sh->k_full[1], kKVTile);
+                    tma_load_2d(sK + kKVTile, &tmK, h * kHD, tok0 + kBK, &sh->k_full[1]);
+                    mbar_expect_tx(&sh->v_full[1], kKVTile);
+                    tma_load_2d(sV + kKVTile, &tmV, h * kHD, tok0 + kBK, &sh->v_full[1]);
                 }
             }
         }
@@ -237,20 +242,20 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
             if (lane == 0) {
                 auto load_k = [&](int j) {
                     const int st = j & 1;
-                    mbar_expect_tx(&sh->k_full[st], kTile);
-                    tma_load_2d(sK + (size_t)st * kTile, &tmK, h * kHD, tok0 + j * kBK, &sh->k_full[st]);
+                    mbar_expect_tx(&sh->k_full[st], kKVTile);
+                    tma_load_2d(sK + (size_t)st * kKVTile, &tmK, h * kHD, tok0 + j * kBK, &sh->k_full[st]);
                 };
                 auto load_v = [&](int j) {
                     const int st = j & 1;
-                    mbar_expect_tx(&sh->v_full[st], kTile);
-                    tma_load_2d(sV + (size_t)st * kTile, &tmV, h * kHD, tok0 + j * kBK, &sh->v_full[st]);
+                    mbar_expect_tx(&sh->v_full[st], kKVTile);
+                    tma_load_2d(sV + (size_t)st * kKVTile, &tmV, h * kHD, tok0 + j * kBK, &sh->v_full[st]);
                 };
                 // (Q and the first two K/V blocks were requested before the CTA-wide set-up)
-                const uint32_t idesc_qk = make_idesc_f16(128, 128);
+                const uint32_t idesc_qk = make_idesc_f16(128, kBK);
                 const uint32_t idesc_pv = make_idesc_f16(128, 64, false, true);   // V is an MN-major B operand
                 const uint32_t qa = smem_u32(sQ);
                 auto issue_qk = [&](int j) {   // S = Q K_j^T into the S columns
-                    const uint32_t ka = smem_u32(sK + (size_t)(j & 1) * kTile);
+                    const uint32_t ka = smem_u32(sK + (size_t)(j & 1) * kKVTile);
 #pragma unroll
                     for (int ks = 0; ks < 4; ++ks)
                         umma_f16(tmem, make_smem_desc(qa + ks * 32, 16, 1024, 2), make_smem_desc(ka + ks * 32, 16, 1024, 2),
@@ -274,16 +279,16 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                     if (!ok) break;
                     AT_STAMP(14 + 2 * j);
                     tc_fence_after();
-                    const uint32_t va = smem_u32(sV + (size_t)st * kTile);
+                    const uint32_t va = smem_u32(sV + (size_t)st * kKVTile);
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)   // P of keys 16ks..16ks+15: 8 packed columns
+                    for (int ks = 0; ks < kBK / 16; ++ks)   // P of keys 16ks..16ks+15: 8 packed columns
                         umma_f16_ts(tmem + kOCol, tmem + kPCol + (uint32_t)(ks * 8), make_smem_desc(va + ks * 2048, 0, 1024, 2),
                                     idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(&sh->pv_done);
                     AT_STAMP(15 + 2 * j);
                     if (j + 1 < nkb) {
-                        // S_{j+1} right behind it: every softmax thread has finished reading S_j (p_ready), and P has
-                        // its own columns, so the next block's maxima are computed while P_j V_j runs
+                        // S_{j+1} right behind it, into the columns that hold P_j: tcgen05 operations execute in issue
+                        // order, so Q K_{j+1}^T cannot overwrite P_j before P_j V_j has read it
                         ok = mbar_wait(&sh->k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u);
                         if (!ok) break;
                         tc_fence_after();
@@ -304,206 +309,131 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
                 }
             }
         } else {
-            // ---- softmax warps: two threads per query row (TMEM lane), each owns 64 of a block's 128 keys
-            const int quarter = warp & 3, half_id = warp >> 2;
+            // ---- softmax warps: one thread per query row (TMEM lane) and key block
+            const int quarter = warp & 3;
             const int row = quarter * 32 + lane;
             const int qr = q0 + row;                       // query index inside the sequence
             const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
             const bool has_mask = p.mask != nullptr;   // uniform: the masked code path is separate from the plain one
             const half* mrow = (has_mask && qr < L) ? p.mask + (size_t)qr * p.mask_ld : nullptr;
             const bool mask_vec = has_mask && (p.mask_ld & 7) == 0 && (reinterpret_cast<uintptr_t>(p.mask) & 15) == 0;
-            const uint32_t s_addr = tmem + lane_base + (uint32_t)(half_id * 64);           // this thread's S columns
-            const uint32_t p_addr = tmem + lane_base + kPCol + (uint32_t)(half_id * 32);   // its 64 keys as packed fp16
-            const uint32_t o_addr = tmem + lane_base + kOCol + (uint32_t)(half_id * 32);   // the O columns it rescales/stores
-            float m_run = -INFINITY, l_run = 0.f;   // running maximum of the row, running sum of this half-row
+            const uint32_t s_addr = tmem + lane_base;           // this row's scores of a block
+            const uint32_t p_addr = tmem + lane_base + kPCol;   // its P values as packed fp16 (over the first half of the score columns)
+            const uint32_t o_addr = tmem + lane_base + kOCol;   // its 64 output columns
+            float m_run = -INFINITY, l_run = 0.f;   // running maximum and running sum of the row
             bool ok = true;
             for (int j = 0; j < nkb; ++j) {
                 int got = 1;
                 if (lane == 0) got = (!sh->abort && mbar_wait(&sh->s_ready, (uint32_t)j & 1u)) ? 1 : 0;
                 got = __shfl_sync(0xffffffffu, got, 0);
                 if (!got) {
-                    // keep the pair barriers balanced: the partner warp may still be inside the loop
                     ok = false;
                     sh->abort = 1;
-                    for (int jj = j; jj < nkb; ++jj) named_pair_sync(1 + quarter);
                     break;
                 }
-                if (tid == 0) AT_STAMP(30 + 4 * j);
+                if (tid == 0) AT_STAMP(30 + 4 * (j & 3));
                 tc_fence_after();
-                const int k0 = j * kBK + half_id * 64;
-                const bool all_valid = k0 + 64 <= valid;   // uniform per warp: no per-key validity selects needed
-                const bool plain = !has_mask && all_valid;
+                const int k0 = j * kBK;
+                const bool plain = !has_mask && k0 + kBK <= valid;   // uniform: no per-key validity selects needed
 
-                // Maximum of the scaled, masked scores of this half-row (log2 domain).
-                auto half_row_max = [&]() -> float {
-                    float bmax = -INFINITY;
-                    if (plain) {
-                        // the common case: both 32-column loads in flight at once, one wait
-                        uint32_t r0[32], r1[32];
-                        tmem_ld32(s_addr, r0);
-                        tmem_ld32(s_addr + 32, r1);
-                        tmem_ld_wait();
-                        float raw0 = -INFINITY, raw1 = -INFINITY;   // the scale is positive: scale the maximum once
+                // The row's 64 scores of this block. S_j could only be computed after P_{j-1} V_{j-1} (issue order), so
+                // O and the P columns are free to be written from here on.
+                uint32_t r[kNCh][32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            raw0 = fmaxf(raw0, __uint_as_float(r0[i]));
-                            raw1 = fmaxf(raw1, __uint_as_float(r1[i]));
-                        }
-                        return fmaxf(raw0, raw1) * p.scale_log2;
+                for (int c = 0; c < kNCh; ++c) tmem_ld32(s_addr + c * 32, r[c]);
+                tmem_ld_wait();
+                // Scaled, masked scores (log2 domain) in place, and their maximum.
+                float bmax = -INFINITY;
+                if (plain) {
+                    float raw[kNCh];   // the scale is positive: scale the maximum once
+#pragma unroll
+                    for (int c = 0; c < kNCh; ++c) raw[c] = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+#pragma unroll
+                        for (int c = 0; c < kNCh; ++c) raw[c] = fmaxf(raw[c], __uint_as_float(r[c][i]));
                     }
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t r[32];
-                        tmem_ld32(s_addr + c * 32, r);
-                        tmem_ld_wait();
-                        const int kc = k0 + c * 32;
-                        if (has_mask) {
-                            float mk[32];
-                            load_mask32(mk, mrow, kc, valid, mask_vec);
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const float v = fmaf(__uint_as_float(r[i]), p.scale_log2, mk[i]);
-                                bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const float v = __uint_as_float(r[i]) * p.scale_log2;
-                                bmax = fmaxf(bmax, (kc + i < valid) ? v : -INFINITY);
-                            }
-                        }
-                    }
-                    return bmax;
-                };
-                // P = 2^(s - shift) as packed fp16 into the P columns; returns the sum of the fp16 values written and,
-                // through `bmax`, the maximum of the scaled, masked scores seen on the way.
-                auto write_p = [&](float shift, float& bmax) -> float {
-                    const float nshift = -shift;
-                    float lsum = 0.f;
-                    bmax = -INFINITY;
-                    if (plain) {
-                        uint32_t r0[32], r1[32];
-                        tmem_ld32(s_addr, r0);
-                        tmem_ld32(s_addr + 32, r1);
-                        tmem_ld_wait();
-                        uint32_t pk[16];
-                        float raw = -INFINITY;
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            raw = fmaxf(raw, fmaxf(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1])));
-                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r0[i]), p.scale_log2, nshift),
-                                                      fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, nshift)));
-                        }
-                        tmem_st16(p_addr, pk);
-                        lsum += sum_packed(pk);
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            raw = fmaxf(raw, fmaxf(__uint_as_float(r1[i]), __uint_as_float(r1[i + 1])));
-                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r1[i]), p.scale_log2, nshift),
-                                                      fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, nshift)));
-                        }
-                        tmem_st16(p_addr + 16, pk);
-                        lsum += sum_packed(pk);
-                        bmax = raw * p.scale_log2;
-                        return lsum;
-                    }
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t r[32];
-                        tmem_ld32(s_addr + c * 32, r);
-                        tmem_ld_wait();
-                        const int kc = k0 + c * 32;
-                        uint32_t pk[16];
-                        if (has_mask) {
-                            float mk[32];
-                            load_mask32(mk, mrow, kc, valid, mask_vec);
-#pragma unroll
-                            for (int i = 0; i < 32; i += 2) {
-                                float va = fmaf(__uint_as_float(r[i]), p.scale_log2, mk[i]);
-                                float vb = fmaf(__uint_as_float(r[i + 1]), p.scale_log2, mk[i + 1]);
-                                va = (kc + i < valid) ? va : -INFINITY;
-                                vb = (kc + i + 1 < valid) ? vb : -INFINITY;
-                                bmax = fmaxf(bmax, fmaxf(va, vb));
-                                pk[i >> 1] = ex2_h2(pack2(va + nshift, vb + nshift));
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; i += 2) {
-                                const float va = (kc + i < valid) ? __uint_as_float(r[i]) * p.scale_log2 : -INFINITY;
-                                const float vb = (kc + i + 1 < valid) ? __uint_as_float(r[i + 1]) * p.scale_log2 : -INFINITY;
-                                bmax = fmaxf(bmax, fmaxf(va, vb));
-                                pk[i >> 1] = ex2_h2(pack2(va + nshift, vb + nshift));
-                            }
-                        }
-                        tmem_st16(p_addr + c * 16, pk);
-                        lsum += sum_packed(pk);
-                    }
-                    return lsum;
-                };
-                // O and the running sum move to a new reference point (O accumulates in tensor memory; each thread
-                // rescales its 32 of the 64 columns). Only called when P_{j-1} V_{j-1} has completed.
-                auto rescale = [&](float alpha) {
-                    l_run *= alpha;
-#pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t r[16];
-                        tmem_ld16(o_addr + c * 16, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st16(o_addr + c * 16, r);
-                    }
-                };
-
-                if (j == 0) {
-                    // first block: row maximum first, it becomes the reference point of the exponentials
-                    float bmax = half_row_max();
-                    sh->xmax[half_id][row] = bmax;
-                    named_pair_sync(1 + quarter);
-                    bmax = fmaxf(bmax, sh->xmax[half_id ^ 1][row]);
-                    if (tid == 0) AT_STAMP(31 + 4 * j);
-                    m_run = bmax;
-                    float unused;
-                    l_run = write_p((m_run == -INFINITY) ? 0.f : m_run, unused);
-                    if (tid == 0) AT_STAMP(32 + 4 * j);
+                    for (int c = 0; c < kNCh; ++c) bmax = fmaxf(bmax, raw[c]);
+                    bmax *= p.scale_log2;
                 } else {
-                    // later blocks: one pass. P is written against the current reference point while the block
-                    // maximum is taken on the way; only if a row's maximum has grown by more than 2^8 (P could leave
-                    // the fp16 range) the reference moves, O is rescaled and the block is done again. The final
-                    // division by the row sum makes the result independent of the reference point.
-                    // P_{j-1} V_{j-1} must have completed before the P columns are written again; it was issued
-                    // before this block's Q K^T, whose completion has just been seen, so this wait does not block.
+#pragma unroll
+                    for (int c = 0; c < kNCh; ++c) {
+                        const int kc = k0 + c * 32;
+                        if (has_mask) {
+                            float mk[32];
+                            load_mask32(mk, mrow, kc, valid, mask_vec);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const float v = fmaf(__uint_as_float(r[c][i]), p.scale_log2, mk[i]);
+                                r[c][i] = __float_as_uint((kc + i < valid) ? v : -INFINITY);
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const float v = __uint_as_float(r[c][i]) * p.scale_log2;
+                                r[c][i] = __float_as_uint((kc + i < valid) ? v : -INFINITY);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, __uint_as_float(r[c][i]));
+                    }
+                }
+                // The reference point of the exponentials moves only when the row maximum has grown by more than 2^8
+                // (P could leave the fp16 range); the final division by the row sum makes the result independent of it.
+                const bool grow = bmax > m_run + kRescaleStep;   // also true for the first finite score of a row
+                if (j > 0) {
+                    // P_{j-1} V_{j-1} has completed (it was issued before this block's Q K^T): the wait does not block
                     int pv = 1;
                     if (lane == 0) pv = (!sh->abort && mbar_wait(&sh->pv_done, (uint32_t)(j - 1) & 1u)) ? 1 : 0;
                     pv = __shfl_sync(0xffffffffu, pv, 0);
                     if (!pv) {
                         ok = false;
                         sh->abort = 1;
-                        for (int jj = j; jj < nkb; ++jj) named_pair_sync(1 + quarter);
                         break;
                     }
                     tc_fence_after();
-                    float bmax;
-                    float lblk = write_p((m_run == -INFINITY) ? 0.f : m_run, bmax);
-                    if (tid == 0) AT_STAMP(31 + 4 * j);
-                    sh->xmax[half_id][row] = bmax;
-                    named_pair_sync(1 + quarter);
-                    bmax = fmaxf(bmax, sh->xmax[half_id ^ 1][row]);
-                    const bool grow = bmax > m_run + kRescaleStep;   // also true when the row had no finite score so far
                     if (__any_sync(0xffffffffu, grow)) {
-                        const float m_new = grow ? bmax : m_run;
-                        const float shift = (m_new == -INFINITY) ? 0.f : m_new;
-                        tmem_st_wait();   // the first version of P is out of the way
-                        rescale(grow ? ex2_fast(m_run - shift) : 1.f);   // 0 when the row had nothing before
-                        m_run = m_new;
-                        float unused;
-                        lblk = write_p(shift, unused);
+                        // O and the running sum move to the new reference point (0 when the row had nothing before)
+                        const float alpha = grow ? ((m_run == -INFINITY) ? 0.f : ex2_fast(m_run - bmax)) : 1.f;
+                        l_run *= alpha;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t o[16];
+                            tmem_ld16(o_addr + c * 16, o);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st16(o_addr + c * 16, o);
+                        }
                     }
-                    l_run += lblk;
-                    if (tid == 0) AT_STAMP(32 + 4 * j);
                 }
+                if (grow) m_run = bmax;
+                if (tid == 0) AT_STAMP(31 + 4 * (j & 3));
+                // P = 2^(s - reference) as packed fp16 over the first 32 score columns; the row sum is the sum of exactly
+                // the fp16 values that are multiplied with V.
+                const float nshift = (m_run == -INFINITY) ? 0.f : -m_run;
+#pragma unroll
+                for (int c = 0; c < kNCh; ++c) {
+                    uint32_t pk[16];
+                    if (plain) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r[c][i]), p.scale_log2, nshift),
+                                                      fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, nshift)));
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            pk[i >> 1] = ex2_h2(pack2(__uint_as_float(r[c][i]) + nshift, __uint_as_float(r[c][i + 1]) + nshift));
+                    }
+                    tmem_st16(p_addr + c * 16, pk);
+                    l_run += sum_packed(pk);
+                }
+                if (tid == 0) AT_STAMP(32 + 4 * (j & 3));
                 tmem_st_wait();
                 tc_fence_before();
                 mbar_arrive(&sh->p_ready);
-                if (tid == 0) AT_STAMP(33 + 4 * j);
+                if (tid == 0) AT_STAMP(33 + 4 * (j & 3));
             }
             // ---- epilogue: O / row sum -> fp16 -> global
             int fin = 1;
@@ -511,15 +441,11 @@ __global__ void __launch_bounds__(kThreads, 2) attention_tc_kernel(const __grid_
             fin = __shfl_sync(0xffffffffu, fin, 0);
             tc_fence_after();
             if (tid == 0) AT_STAMP(50);
-            // the row sum is the sum of the two half-rows (both are on the scale of the common running maximum)
-            sh->xmax[half_id][row] = l_run;
-            named_pair_sync(1 + quarter);
             if (fin) {
-                const float l = l_run + sh->xmax[half_id ^ 1][row];
-                const float inv = l > 0.f ? 1.f / l : 0.f;
-                half* zrow = p.Z + (size_t)(tok0 + qr) * p.z_pitch + h * kHD + half_id * 32;
+                const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+                half* zrow = p.Z + (size_t)(tok0 + qr) * p.z_pitch + h * kHD;
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < 4; ++c) {
                     uint32_t r[16];
                     tmem_ld16(o_addr + c * 16, r);
                     tmem_ld_wait();
@@ -617,7 +543,7 @@ int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, in
     p.scale_log2 = kLog2e / sqrtf((float)kHD);
     p.err = err_word;
     p.prof = g_attn_prof;
-    const size_t smem = (size_t)kTile * 5 + sizeof(TcShared) + 1024;
+    const size_t smem = (size_t)kTile + 4 * (size_t)kKVTile + sizeof(TcShared) + 1024;
     static PerDeviceOnce once;
     const cudaError_t attr_err = once.run([] {
         return cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
