@@ -5,12 +5,15 @@
 //
 // A CTA owns 128 queries of one head of one sequence, one TMEM lane and one thread per query:
 //   S_j = Q K_j^T      SS UMMA 128x64x16 (x4), Q and the 64-key block K_j in shared memory (TMA, 128-byte
-//                      swizzle), fp32 S_j in 64 TMEM columns
-//   softmax            four warps, one thread per query row, one pass per block: tcgen05.ld of the row's 64 scores,
-//                      scale (log2 domain), additive mask, key validity, row maximum; if the maximum has grown by
-//                      more than 2^8 the reference point moves and O is rescaled in place; P_j = 2^(s - reference) as
-//                      packed fp16 over the first 32 score columns (tcgen05.st), row sum in fp32. No exchange
-//                      between threads, no second pass
+//                      swizzle), S_j accumulated in fp16 (as the reference's kernels accumulate their scores) in 64
+//                      TMEM columns
+//   softmax            four warps, one thread per query row, one pass per block: the row's 64 scores come out of
+//                      tensor memory two to a register (tcgen05.ld.pack::16b); row maximum, scale and reference point
+//                      (log2 domain) and the exponentials in packed fp16 arithmetic, no conversion; additive mask
+//                      and key validity in fp32 where a block needs them; if the maximum has grown by more than 2^8
+//                      the reference point moves and O is rescaled in place; P_j = 2^(s - reference) as packed fp16
+//                      over the first 32 score columns (tcgen05.st), row sum in fp32. No exchange between threads,
+//                      no second pass
 //   O += P_j V_j       TS UMMA 128x64x16 (x4): A = P_j read from tensor memory, B = V_j in shared memory as loaded
 //                      (rows = keys), used as an MN-major operand; Q K_{j+1}^T is issued right behind it into the
 //                      columns that hold P_j (tcgen05 operations execute in issue order)
@@ -29,21 +32,22 @@ namespace et {
 
 namespace {
 
-// Keys per block: 64 (four CTAs per SM) or 128 (two). Measured at 256 x 512 tokens, 16 heads: 731 us against 812 us;
-// with two threads per row and three CTAs per SM 801 us; the earlier two-pass form with 128 keys, two threads per row
-// and two CTAs per SM 767 us. Sixteen resident softmax warps with the shortest hand-overs between them win.
-#ifndef ET_ATTN_BK
-#define ET_ATTN_BK 64
-#endif
-constexpr int kBQ = 128, kBK = ET_ATTN_BK, kHD = 64;
-static_assert(kBK == 64 || kBK == 128, "key blocks of 64 or 128");
+// 64 keys per block and one thread per query row, four CTAs per SM. Measured at 256 x 512 tokens, 16 heads, with fp32
+// scores: 731 us; 128 keys and two CTAs per SM 812 us; two threads per row and three CTAs per SM 801 us; the earlier
+// two-pass form with 128 keys, two threads per row and two CTAs per SM 767 us. Sixteen resident softmax warps with
+// the shortest hand-overs between them win. With fp16 scores (below) 597 us.
+constexpr int kBQ = 128, kBK = 64, kHD = 64;
 constexpr int kNCh = kBK / 32;            // 32-column chunks of a score row
+// Q K^T accumulated in fp16, as the reference's kernels do (kernels/attention.cu:82: c_t<half>): the scores come out
+// of tensor memory already packed two to a register, so the common pass needs no fp32 -> fp16 conversion (half of its
+// work on the conversion / special-function pipe) and half the registers.
+constexpr bool kScoresF16 = true;
 constexpr int kTile = kBQ * kHD * 2;      // 16 KB: the 128 x 64 fp16 Q tile
 constexpr int kKVTile = kBK * kHD * 2;    // one key block of K or V
 constexpr int kSoftmaxWarps = 4;          // one thread per query row
 constexpr int kThreads = 32 * (kSoftmaxWarps + 1);   // + 1 warp whose lane 0 issues TMA and UMMA
-constexpr int kCtasPerSm = kBK == 64 ? 4 : 2;
-constexpr int kTmemCols = kBK + 64 <= 128 ? 128 : 256;   // S (P overlays its first half) | O 64
+constexpr int kCtasPerSm = 4;
+constexpr int kTmemCols = 128;            // S 64 (P overlays its first 32 columns) | O 64: four CTAs share an SM's tensor memory
 constexpr uint32_t kPCol = 0, kOCol = kBK;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleStep = 8.f;       // log2 units by which a row maximum must grow before O is rescaled
@@ -251,7 +255,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
                     tma_load_2d(sV + (size_t)st * kKVTile, &tmV, h * kHD, tok0 + j * kBK, &sh->v_full[st]);
                 };
                 // (Q and the first two K/V blocks were requested before the CTA-wide set-up)
-                const uint32_t idesc_qk = make_idesc_f16(128, kBK);
+                const uint32_t idesc_qk = make_idesc_f16(128, kBK, false, false, kScoresF16);
                 const uint32_t idesc_pv = make_idesc_f16(128, 64, false, true);   // V is an MN-major B operand
                 const uint32_t qa = smem_u32(sQ);
                 auto issue_qk = [&](int j) {   // S = Q K_j^T into the S columns
@@ -338,47 +342,53 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
 
                 // The row's 64 scores of this block. S_j could only be computed after P_{j-1} V_{j-1} (issue order), so
                 // O and the P columns are free to be written from here on.
-                uint32_t r[kNCh][32];
-#pragma unroll
-                for (int c = 0; c < kNCh; ++c) tmem_ld32(s_addr + c * 32, r[c]);
+                uint32_t rp[32];   // the row's 64 fp16 scores, two to a register
+                tmem_ld32_pack16(s_addr, rp);
                 tmem_ld_wait();
-                // Scaled, masked scores (log2 domain) in place, and their maximum.
+                // The general pass (additive mask, keys beyond the valid length): the scaled, masked scores (log2 domain)
+                // of one 32-column chunk in fp32. It is evaluated twice per block, for the maximum and for P, so that
+                // only the packed scores stay in registers in between.
+                auto general_chunk = [&](int c, float (&v)[32]) {
+                    const int kc = k0 + c * 32;
+                    if (has_mask) {
+                        float mk[32];
+                        load_mask32(mk, mrow, kc, valid, mask_vec);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float2 f = __half22float2(*reinterpret_cast<const half2*>(&rp[c * 16 + i]));
+                            v[2 * i] = (kc + 2 * i < valid) ? fmaf(f.x, p.scale_log2, mk[2 * i]) : -INFINITY;
+                            v[2 * i + 1] = (kc + 2 * i + 1 < valid) ? fmaf(f.y, p.scale_log2, mk[2 * i + 1]) : -INFINITY;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float2 f = __half22float2(*reinterpret_cast<const half2*>(&rp[c * 16 + i]));
+                            v[2 * i] = (kc + 2 * i < valid) ? f.x * p.scale_log2 : -INFINITY;
+                            v[2 * i + 1] = (kc + 2 * i + 1 < valid) ? f.y * p.scale_log2 : -INFINITY;
+                        }
+                    }
+                };
                 float bmax = -INFINITY;
                 if (plain) {
-                    float raw[kNCh];   // the scale is positive: scale the maximum once
+                    half2 mx0 = *reinterpret_cast<const half2*>(&rp[0]), mx1 = *reinterpret_cast<const half2*>(&rp[1]);
 #pragma unroll
-                    for (int c = 0; c < kNCh; ++c) raw[c] = -INFINITY;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-#pragma unroll
-                        for (int c = 0; c < kNCh; ++c) raw[c] = fmaxf(raw[c], __uint_as_float(r[c][i]));
+                    for (int i = 2; i < 32; i += 2) {
+                        mx0 = __hmax2(mx0, *reinterpret_cast<const half2*>(&rp[i]));
+                        mx1 = __hmax2(mx1, *reinterpret_cast<const half2*>(&rp[i + 1]));
                     }
-#pragma unroll
-                    for (int c = 0; c < kNCh; ++c) bmax = fmaxf(bmax, raw[c]);
-                    bmax *= p.scale_log2;
+                    const float2 f = __half22float2(__hmax2(mx0, mx1));
+                    bmax = fmaxf(f.x, f.y) * p.scale_log2;   // the scale is positive: scale the maximum once
                 } else {
 #pragma unroll
                     for (int c = 0; c < kNCh; ++c) {
-                        const int kc = k0 + c * 32;
-                        if (has_mask) {
-                            float mk[32];
-                            load_mask32(mk, mrow, kc, valid, mask_vec);
+                        float v[32];
+                        general_chunk(c, v);
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const float v = fmaf(__uint_as_float(r[c][i]), p.scale_log2, mk[i]);
-                                r[c][i] = __float_as_uint((kc + i < valid) ? v : -INFINITY);
-                            }
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                const float v = __uint_as_float(r[c][i]) * p.scale_log2;
-                                r[c][i] = __float_as_uint((kc + i < valid) ? v : -INFINITY);
-                            }
-                        }
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, __uint_as_float(r[c][i]));
+                        for (int i = 0; i < 32; ++i) bmax = fmaxf(bmax, v[i]);
                     }
                 }
+                // The reference point is kept representable in fp16 (the packed pass subtracts it in fp16), within range.
+                if (bmax > -INFINITY) bmax = __half2float(__float2half_rn(fminf(fmaxf(bmax, -60000.f), 60000.f)));
                 // The reference point of the exponentials moves only when the row maximum has grown by more than 2^8
                 // (P could leave the fp16 range); the final division by the row sum makes the result independent of it.
                 const bool grow = bmax > m_run + kRescaleStep;   // also true for the first finite score of a row
@@ -417,14 +427,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
                 for (int c = 0; c < kNCh; ++c) {
                     uint32_t pk[16];
                     if (plain) {
+                        const half2 sc2 = __float2half2_rn(p.scale_log2), sh2 = __float2half2_rn(nshift);
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(r[c][i]), p.scale_log2, nshift),
-                                                      fmaf(__uint_as_float(r[c][i + 1]), p.scale_log2, nshift)));
+                        for (int i = 0; i < 16; ++i) {
+                            const half2 a2 = __hfma2(*reinterpret_cast<const half2*>(&rp[c * 16 + i]), sc2, sh2);
+                            pk[i] = ex2_h2(*reinterpret_cast<const uint32_t*>(&a2));
+                        }
                     } else {
+                        float v[32];
+                        general_chunk(c, v);
 #pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            pk[i >> 1] = ex2_h2(pack2(__uint_as_float(r[c][i]) + nshift, __uint_as_float(r[c][i + 1]) + nshift));
+                        for (int i = 0; i < 32; i += 2) pk[i >> 1] = ex2_h2(pack2(v[i] + nshift, v[i + 1] + nshift));
                     }
                     tmem_st16(p_addr + c * 16, pk);
                     l_run += sum_packed(pk);
