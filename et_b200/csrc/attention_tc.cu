@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
             mbar_init(&sh->q_full, 1);
             for (int j = 0; j < 2; ++j) { mbar_init(&sh->k_full[j], 1); mbar_init(&sh->v_full[j], 1); }
             mbar_init(&sh->s_ready, 1);
-            mbar_init(&sh->p_ready, 32 * kSoftmaxWarps);
+            mbar_init(&sh->p_ready, kSoftmaxWarps);   // one arrive per softmax warp
             mbar_init(&sh->pv_done, 1);
             mbar_init(&sh->o_done, 1);
             sh->abort = 0;
@@ -393,16 +393,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
                 // (P could leave the fp16 range); the final division by the row sum makes the result independent of it.
                 const bool grow = bmax > m_run + kRescaleStep;   // also true for the first finite score of a row
                 if (j > 0) {
-                    // P_{j-1} V_{j-1} has completed (it was issued before this block's Q K^T): the wait does not block
-                    int pv = 1;
-                    if (lane == 0) pv = (!sh->abort && mbar_wait(&sh->pv_done, (uint32_t)(j - 1) & 1u)) ? 1 : 0;
-                    pv = __shfl_sync(0xffffffffu, pv, 0);
-                    if (!pv) {
-                        ok = false;
-                        sh->abort = 1;
-                        break;
-                    }
-                    tc_fence_after();
+                    // P_{j-1} V_{j-1} has completed: it was issued before this block's Q K^T by the same thread, and the
+                    // commit that signalled S_j covers every earlier operation of that thread.
                     if (__any_sync(0xffffffffu, grow)) {
                         // O and the running sum move to the new reference point (0 when the row had nothing before)
                         const float alpha = grow ? ((m_run == -INFINITY) ? 0.f : ex2_fast(m_run - bmax)) : 1.f;
@@ -445,7 +437,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
                 if (tid == 0) AT_STAMP(32 + 4 * (j & 3));
                 tmem_st_wait();
                 tc_fence_before();
-                mbar_arrive(&sh->p_ready);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->p_ready);
                 if (tid == 0) AT_STAMP(33 + 4 * (j & 3));
             }
             // ---- epilogue: O / row sum -> fp16 -> global
