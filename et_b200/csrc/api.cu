@@ -65,6 +65,14 @@ extern "C" int et_set_tuning_goal(int goal) {
     return ET_OK;
 }
 
+namespace et { void attention_tc_set_scores_fp32(int on); int attention_tc_scores_fp32(); }
+extern "C" int et_set_attention_scores_fp32(int on) {
+    if (on != 0 && on != 1) return et::fail(ET_ERR_INVALID, "et_set_attention_scores_fp32: 0 (fp16 scores) or 1 (fp32 scores)");
+    et::attention_tc_set_scores_fp32(on);
+    return ET_OK;
+}
+extern "C" int et_attention_scores_fp32(void) { return et::attention_tc_scores_fp32(); }
+
 // Not part of the public header: used by profiling builds of the library only.
 extern "C" int et_debug_set_gemm_profile_buffer(void* dev_buf) {
     et::tile_gemm_set_profile_buffer(static_cast<long long*>(dev_buf));

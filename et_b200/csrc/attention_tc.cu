@@ -38,10 +38,11 @@ namespace {
 // the shortest hand-overs between them win. With fp16 scores (below) 597 us.
 constexpr int kBQ = 128, kBK = 64, kHD = 64;
 constexpr int kNCh = kBK / 32;            // 32-column chunks of a score row
-// Q K^T accumulated in fp16, as the reference's kernels do (kernels/attention.cu:82: c_t<half>): the scores come out
-// of tensor memory already packed two to a register, so the common pass needs no fp32 -> fp16 conversion (half of its
-// work on the conversion / special-function pipe) and half the registers.
-constexpr bool kScoresF16 = true;
+// The kernel is a template on how Q K^T is accumulated. fp16, as the reference's kernels do (kernels/attention.cu:82:
+// c_t<half>), is the default: the scores come out of tensor memory already packed two to a register, the common pass
+// needs no fp32 -> fp16 conversion and half the registers. Its error grows with the size of the scores (one fp16
+// rounding of each 16-term partial sum): against exact arithmetic 2e-3 in the worst element for |q.k| up to 50, 1.4e-2
+// up to 165, 3e-2 up to 390. fp32 (attention_tc_set_scores_fp32) keeps 2e-3 throughout and takes ~1.5 times as long.
 constexpr int kTile = kBQ * kHD * 2;      // 16 KB: the 128 x 64 fp16 Q tile
 constexpr int kKVTile = kBK * kHD * 2;    // one key block of K or V
 constexpr int kSoftmaxWarps = 4;          // one thread per query row
@@ -138,6 +139,7 @@ __device__ __forceinline__ void load_mask32(float (&mk)[32], const half* mrow, i
     }
 }
 
+template <bool kScoresF16>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ,
                                                                   const __grid_constant__ CUtensorMap tmK,
                                                                   const __grid_constant__ CUtensorMap tmV,
@@ -342,9 +344,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
 
                 // The row's 64 scores of this block. S_j could only be computed after P_{j-1} V_{j-1} (issue order), so
                 // O and the P columns are free to be written from here on.
-                uint32_t rp[32];   // the row's 64 fp16 scores, two to a register
-                tmem_ld32_pack16(s_addr, rp);
+                uint32_t rp[32];        // fp16 scores: the row's 64 scores, two to a register
+                uint32_t rf[kNCh][32];  // fp32 scores
+                if constexpr (kScoresF16) {
+                    tmem_ld32_pack16(s_addr, rp);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < kNCh; ++c) tmem_ld32(s_addr + c * 32, rf[c]);
+                }
                 tmem_ld_wait();
+                // scores 2i and 2i+1 of chunk c as fp32
+                auto score2 = [&](int c, int i) -> float2 {
+                    if constexpr (kScoresF16) return __half22float2(*reinterpret_cast<const half2*>(&rp[c * 16 + i]));
+                    else return make_float2(__uint_as_float(rf[c][2 * i]), __uint_as_float(rf[c][2 * i + 1]));
+                };
                 // The general pass (additive mask, keys beyond the valid length): the scaled, masked scores (log2 domain)
                 // of one 32-column chunk in fp32. It is evaluated twice per block, for the maximum and for P, so that
                 // only the packed scores stay in registers in between.
@@ -355,21 +368,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
                         load_mask32(mk, mrow, kc, valid, mask_vec);
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const float2 f = __half22float2(*reinterpret_cast<const half2*>(&rp[c * 16 + i]));
+                            const float2 f = score2(c, i);
                             v[2 * i] = (kc + 2 * i < valid) ? fmaf(f.x, p.scale_log2, mk[2 * i]) : -INFINITY;
                             v[2 * i + 1] = (kc + 2 * i + 1 < valid) ? fmaf(f.y, p.scale_log2, mk[2 * i + 1]) : -INFINITY;
                         }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
-                            const float2 f = __half22float2(*reinterpret_cast<const half2*>(&rp[c * 16 + i]));
+                            const float2 f = score2(c, i);
                             v[2 * i] = (kc + 2 * i < valid) ? f.x * p.scale_log2 : -INFINITY;
                             v[2 * i + 1] = (kc + 2 * i + 1 < valid) ? f.y * p.scale_log2 : -INFINITY;
                         }
                     }
                 };
                 float bmax = -INFINITY;
-                if (plain) {
+                if (plain && kScoresF16) {
                     half2 mx0 = *reinterpret_cast<const half2*>(&rp[0]), mx1 = *reinterpret_cast<const half2*>(&rp[1]);
 #pragma unroll
                     for (int i = 2; i < 32; i += 2) {
@@ -378,6 +391,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
                     }
                     const float2 f = __half22float2(__hmax2(mx0, mx1));
                     bmax = fmaxf(f.x, f.y) * p.scale_log2;   // the scale is positive: scale the maximum once
+                } else if (plain) {
+                    float raw[kNCh];
+#pragma unroll
+                    for (int c = 0; c < kNCh; ++c) raw[c] = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+#pragma unroll
+                        for (int c = 0; c < kNCh; ++c) raw[c] = fmaxf(raw[c], __uint_as_float(rf[c][i]));
+                    }
+#pragma unroll
+                    for (int c = 0; c < kNCh; ++c) bmax = fmaxf(bmax, raw[c]);
+                    bmax *= p.scale_log2;
                 } else {
 #pragma unroll
                     for (int c = 0; c < kNCh; ++c) {
@@ -418,13 +443,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
 #pragma unroll
                 for (int c = 0; c < kNCh; ++c) {
                     uint32_t pk[16];
-                    if (plain) {
+                    if (plain && kScoresF16) {
                         const half2 sc2 = __float2half2_rn(p.scale_log2), sh2 = __float2half2_rn(nshift);
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             const half2 a2 = __hfma2(*reinterpret_cast<const half2*>(&rp[c * 16 + i]), sc2, sh2);
                             pk[i] = ex2_h2(*reinterpret_cast<const uint32_t*>(&a2));
                         }
+                    } else if (plain) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            pk[i >> 1] = ex2_h2(pack2(fmaf(__uint_as_float(rf[c][i]), p.scale_log2, nshift),
+                                                      fmaf(__uint_as_float(rf[c][i + 1]), p.scale_log2, nshift)));
                     } else {
                         float v[32];
                         general_chunk(c, v);
@@ -487,6 +517,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
 }
 
 long long* g_attn_prof = nullptr;
+bool g_scores_fp32 = false;   // how Q K^T is accumulated (see kScoresF16 above); process-wide, read at launch
 
 // Error word of the kernel's bounded waits: a device variable of the library image (one copy per device that
 // loads the library, zero at load), so that no launch ever allocates. The kernel writes it only when a wait
@@ -552,15 +583,21 @@ int attention_tc_launch(half* Z, const half* Q, const half* K, const half* V, in
     const size_t smem = (size_t)kTile + 4 * (size_t)kKVTile + sizeof(TcShared) + 1024;
     static PerDeviceOnce once;
     const cudaError_t attr_err = once.run([] {
-        return cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+        if (e != cudaSuccess) return e;
+        return cudaFuncSetAttribute(attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
     });
     if (attr_err != cudaSuccess) return cuda_status(attr_err, "attention: shared memory opt-in");
     const int nblk = cu_seqlens ? (total_tokens + kBQ - 1) / kBQ + batch : batch * ((uniform_len + kBQ - 1) / kBQ);
-    return cuda_status(launch_pdl(attention_tc_kernel, dim3(nblk, nhead), dim3(kThreads), smem, st, tq, tk, tv, p),
+    auto kernel = g_scores_fp32 ? attention_tc_kernel<false> : attention_tc_kernel<true>;
+    return cuda_status(launch_pdl(kernel, dim3(nblk, nhead), dim3(kThreads), smem, st, tq, tk, tv, p),
                        "attention (tcgen05) launch");
 }
 
 void attention_tc_set_profile_buffer(long long* dev_buf) { g_attn_prof = dev_buf; }
+
+void attention_tc_set_scores_fp32(int on) { g_scores_fp32 = on != 0; }
+int attention_tc_scores_fp32() { return g_scores_fp32 ? 1 : 0; }
 
 // Reads and clears the current device's error word of the tcgen05 attention kernel (synchronises).
 // 0 = no wait gave up since the last read.

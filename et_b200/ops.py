@@ -15,6 +15,7 @@ __all__ = [
     "gen_sparse_tile_mat", "gen_sparse_row_mat", "build_head_ptr", "Encoder", "encoder_buffer_size",
     "encoder_batch_buffer_size", "KIND_TILE", "KIND_PRUNE", "KIND_LENGTH", "KIND_PRUNE_QKV",
     "Model", "attention_check", "prune_dense_to_tiles", "select_rows_magnitude", "compact_rows", "set_tuning_goal",
+    "set_attention_scores_fp32", "attention_scores_fp32",
 ]
 
 _i = ctypes.c_int
@@ -41,6 +42,16 @@ def set_tuning_goal(goal):
     """"latency" (default): weights created afterwards are packed for the shortest single launch; "throughput": for
     the least SM time per launch (several independent batches in flight on separate streams)."""
     check(lib().et_set_tuning_goal(_i({"latency": 0, "throughput": 1}[goal])))
+
+
+def set_attention_scores_fp32(on):
+    """False (default): the tcgen05 attention kernel accumulates Q K^T in fp16, as the reference's kernels do; True: in
+    fp32 (for models whose attention logits are large; ~1.5 times the time). Process-wide, read at launch."""
+    check(lib().et_set_attention_scores_fp32(_i(1 if on else 0)))
+
+
+def attention_scores_fp32():
+    return bool(lib().et_attention_scores_fp32())
 
 
 class TileWeight:

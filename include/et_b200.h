@@ -66,6 +66,13 @@ int et_tile_weight_check(const et_tile_weight* w, int* code);
 #define ET_GOAL_LATENCY 0
 #define ET_GOAL_THROUGHPUT 1
 int et_set_tuning_goal(int goal);
+/* Extension: how the tcgen05 attention kernel accumulates Q K^T. 0 (default): in fp16, as the reference's kernels
+ * accumulate their scores (kernels/attention.cu:82, `c_t<half>`); the error against exact arithmetic grows with the
+ * size of the scores (worst output element: 2e-3 for |q.k| up to 50, 1.4e-2 up to 165, 3e-2 up to 390). 1: in fp32
+ * (2e-3 throughout, ~1.5 times the time). Process-wide, read when a launch is issued: graphs recorded earlier by
+ * et_encoder_run_batch / et_model_run_batch keep the kernel they were recorded with. */
+int et_set_attention_scores_fp32(int on);
+int et_attention_scores_fp32(void);
 /* info[6] = {block_rows_per_cta, n_chunks, k_chunks, stages, stage_bytes, packed_bytes}. */
 int et_tile_weight_info(const et_tile_weight* w, int* info);
 /* Same contraction from DEVICE-resident tile arrays, K = in_feat explicit. The packed form of a

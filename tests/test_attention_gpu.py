@@ -49,6 +49,30 @@ def test_attention_otf(et, orc, L, d, H, use_mask):
     util.assert_close(host(out), want, what=f"otf attention L={L}")
 
 
+@pytest.mark.parametrize("scale,fp32_scores,max_abs,mean_abs", [(1.0, False, 4e-3, 2e-4), (1.0, True, 4e-3, 2e-4),
+                                                                  (3.0, True, 6e-3, 4e-4), (3.0, False, 6e-2, 3e-3)])
+def test_attention_score_precision(et, orc, scale, fp32_scores, max_abs, mean_abs):
+    """Q K^T accumulated in fp16 (the default, as the reference does) or in fp32: with unit-variance operands
+    (|q.k| up to ~45) both stay within a fifth of the parity tolerance; with operands three times larger (|q.k| up to
+    ~390, softmax close to one-hot) the fp32 form still does and the fp16 form is allowed the error of rounding the
+    scores to fp16."""
+    L, d, H = 512, 768, 12
+    Q, K, V = _qkv(1, L, d)
+    Q = (Q.astype(np.float32) * scale).astype(np.float16)
+    K = (K.astype(np.float32) * scale).astype(np.float16)
+    want = orc.attention(Q, K, V, [L], d, H)
+    assert not et.attention_scores_fp32()
+    et.set_attention_scores_fp32(fp32_scores)
+    try:
+        assert et.attention_scores_fp32() == fp32_scores
+        out = torch.full((L, d), float("nan"), dtype=torch.float16, device="cuda")
+        et.attention_otf(out, dev(Q), dev(K), dev(V), None, L, d, H)
+        torch.cuda.synchronize()
+    finally:
+        et.set_attention_scores_fp32(False)
+    util.assert_close(host(out), want, max_abs=max_abs, mean_abs=mean_abs, what=f"scores fp32={fp32_scores}, scale {scale}")
+
+
 def test_attention_otf_matches_reference_kernel_in_base2_mode(et, orc, ref):
     """The shipped kernel exponentiates in base 2 and floors the row max at 0; with its scale multiplied by
     log2(e) and scores that stay positive-max it computes a true softmax, comparable with ours."""
