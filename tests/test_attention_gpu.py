@@ -35,7 +35,8 @@ def _qkv(seed, T, d, std=1.0):
 
 @pytest.mark.parametrize("L,d,H,use_mask", [(128, 768, 12, False), (128, 768, 12, True), (256, 768, 12, True),
                                             (512, 1024, 16, False), (16, 128, 2, True), (77, 768, 12, True),
-                                            (1, 64, 1, False), (200, 256, 8, False)])
+                                            (1, 64, 1, False), (200, 256, 8, False), (2048, 128, 2, False),
+                                            (1100, 128, 2, True)])
 def test_attention_otf(et, orc, L, d, H, use_mask):
     Q, K, V = _qkv(1, L, d)
     mask = None
