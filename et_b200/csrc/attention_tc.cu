@@ -245,75 +245,82 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
 
     if (b >= 0 && nkb > 0) {
         if (warp == kSoftmaxWarps) {
-            if (lane == 0) {
-                auto load_k = [&](int j) {
-                    const int st = j & 1;
-                    mbar_expect_tx(&sh->k_full[st], kKVTile);
-                    tma_load_2d(sK + (size_t)st * kKVTile, &tmK, h * kHD, tok0 + j * kBK, &sh->k_full[st]);
-                };
-                auto load_v = [&](int j) {
-                    const int st = j & 1;
-                    mbar_expect_tx(&sh->v_full[st], kKVTile);
-                    tma_load_2d(sV + (size_t)st * kKVTile, &tmV, h * kHD, tok0 + j * kBK, &sh->v_full[st]);
-                };
-                // (Q and the first two K/V blocks were requested before the CTA-wide set-up)
-                const uint32_t idesc_qk = make_idesc_f16(128, kBK, false, false, kScoresF16);
-                const uint32_t idesc_pv = make_idesc_f16(128, 64, false, true);   // V is an MN-major B operand
-                const uint32_t qa = smem_u32(sQ);
-                auto issue_qk = [&](int j) {   // S = Q K_j^T into the S columns
-                    const uint32_t ka = smem_u32(sK + (size_t)(j & 1) * kKVTile);
+            // ---- the issuing warp stays converged: every lane waits on the barriers, one elected lane issues the copies
+            // and the UMMAs (tcgen05 instructions issued from a divergent branch are slower)
+            auto load_k = [&](int j) {
+                const int st = j & 1;
+                mbar_expect_tx(&sh->k_full[st], kKVTile);
+                tma_load_2d(sK + (size_t)st * kKVTile, &tmK, h * kHD, tok0 + j * kBK, &sh->k_full[st]);
+            };
+            auto load_v = [&](int j) {
+                const int st = j & 1;
+                mbar_expect_tx(&sh->v_full[st], kKVTile);
+                tma_load_2d(sV + (size_t)st * kKVTile, &tmV, h * kHD, tok0 + j * kBK, &sh->v_full[st]);
+            };
+            // (Q and the first two K/V blocks were requested before the CTA-wide set-up)
+            const uint32_t idesc_qk = make_idesc_f16(128, kBK, false, false, kScoresF16);
+            const uint32_t idesc_pv = make_idesc_f16(128, 64, false, true);   // V is an MN-major B operand
+            const uint32_t qa = smem_u32(sQ);
+            auto issue_qk = [&](int j) {   // S = Q K_j^T into the S columns
+                const uint32_t ka = smem_u32(sK + (size_t)(j & 1) * kKVTile);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks)
-                        umma_f16(tmem, make_smem_desc(qa + ks * 32, 16, 1024, 2), make_smem_desc(ka + ks * 32, 16, 1024, 2),
-                                 idesc_qk, ks > 0);
-                    umma_commit(&sh->s_ready);
-                };
-                AT_STAMP(10);
-                bool ok = mbar_wait(&sh->q_full, 0) && mbar_wait(&sh->k_full[0], 0);
-                AT_STAMP(11);
-                if (ok) {
-                    tc_fence_after();
-                    issue_qk(0);
-                    AT_STAMP(13);
-                }
-                for (int j = 0; j < nkb && ok; ++j) {
-                    const int st = j & 1;
-                    const uint32_t ph = (uint32_t)(j >> 1) & 1u;
-                    if (sh->abort) { ok = false; break; }
-                    // O += P_j V_j once the softmax warps have written P_j (and rescaled O)
-                    ok = mbar_wait(&sh->p_ready, (uint32_t)j & 1u) && mbar_wait(&sh->v_full[st], ph);
-                    if (!ok) break;
-                    AT_STAMP(14 + 2 * j);
-                    tc_fence_after();
+                for (int ks = 0; ks < 4; ++ks)
+                    umma_f16(tmem, make_smem_desc(qa + ks * 32, 16, 1024, 2), make_smem_desc(ka + ks * 32, 16, 1024, 2),
+                             idesc_qk, ks > 0);
+                umma_commit(&sh->s_ready);
+            };
+            if (lane == 0) AT_STAMP(10);
+            bool ok = mbar_wait(&sh->q_full, 0) && mbar_wait(&sh->k_full[0], 0);
+            if (lane == 0) AT_STAMP(11);
+            if (ok) {
+                tc_fence_after();
+                if (elect_one()) issue_qk(0);
+                if (lane == 0) AT_STAMP(13);
+            }
+            for (int j = 0; j < nkb && ok; ++j) {
+                const int st = j & 1;
+                const uint32_t ph = (uint32_t)(j >> 1) & 1u;
+                if (sh->abort) { ok = false; break; }
+                // O += P_j V_j once the softmax warps have written P_j (and rescaled O)
+                ok = mbar_wait(&sh->p_ready, (uint32_t)j & 1u) && mbar_wait(&sh->v_full[st], ph);
+                if (!ok) break;
+                if (lane == 0) AT_STAMP(14 + 2 * j);
+                tc_fence_after();
+                if (elect_one()) {
                     const uint32_t va = smem_u32(sV + (size_t)st * kKVTile);
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks)   // P of keys 16ks..16ks+15: 8 packed columns
                         umma_f16_ts(tmem + kOCol, tmem + kPCol + (uint32_t)(ks * 8), make_smem_desc(va + ks * 2048, 0, 1024, 2),
                                     idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
                     umma_commit(&sh->pv_done);
-                    AT_STAMP(15 + 2 * j);
-                    if (j + 1 < nkb) {
-                        // S_{j+1} right behind it, into the columns that hold P_j: tcgen05 operations execute in issue
-                        // order, so Q K_{j+1}^T cannot overwrite P_j before P_j V_j has read it
-                        ok = mbar_wait(&sh->k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u);
-                        if (!ok) break;
-                        tc_fence_after();
+                }
+                if (lane == 0) AT_STAMP(15 + 2 * j);
+                if (j + 1 < nkb) {
+                    // S_{j+1} right behind it, into the columns that hold P_j: tcgen05 operations execute in issue
+                    // order, so Q K_{j+1}^T cannot overwrite P_j before P_j V_j has read it
+                    ok = mbar_wait(&sh->k_full[(j + 1) & 1], (uint32_t)((j + 1) >> 1) & 1u);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (elect_one()) {
                         issue_qk(j + 1);
-                        if (j + 2 < nkb) {
-                            load_k(j + 2);   // K_j's stage: Q K_j^T completed before the softmax of block j began
-                            // V_j's stage is free once P_j V_j has completed
-                            ok = mbar_wait(&sh->pv_done, (uint32_t)j & 1u);
-                            if (!ok) break;
-                            load_v(j + 2);
-                        }
+                        if (j + 2 < nkb) load_k(j + 2);   // K_j's stage: Q K_j^T completed before the softmax of block j began
+                    }
+                    if (j + 2 < nkb) {
+                        // V_j's stage is free once P_j V_j has completed
+                        ok = mbar_wait(&sh->pv_done, (uint32_t)j & 1u);
+                        if (!ok) break;
+                        if (elect_one()) load_v(j + 2);
                     }
                 }
+            }
+            if (elect_one()) {
                 umma_commit(&sh->o_done);
                 if (!ok) {
                     atomicExch(p.err, 21);
                     sh->abort = 1;
                 }
             }
+            __syncwarp();
         } else {
             // ---- softmax warps: one thread per query row (TMEM lane) and key block
             const int quarter = warp & 3;

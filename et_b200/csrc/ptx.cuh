@@ -28,6 +28,13 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                  "r"(bytes)
                  : "memory");
 }
+// One lane of a converged warp (tcgen05 instructions are issued under this predicate, not from a divergent branch).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}"
+                 : "=r"(pred));
+    return pred != 0;
+}
 // Brings a tensor map (a kernel parameter) into the descriptor cache ahead of the first copy that uses it.
 __device__ __forceinline__ void prefetch_tmap(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");

@@ -83,12 +83,6 @@ struct GemmParams {
 #define ET_STAMP(slot) do { } while (0)
 #endif
 
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile("{\n.reg .pred P;\nelect.sync _|P, 0xffffffff;\nselp.u32 %0, 1, 0, P;\n}"
-                 : "=r"(pred));
-    return pred != 0;
-}
 __device__ __forceinline__ void tc_cp_128x256b(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
