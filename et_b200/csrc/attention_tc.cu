@@ -336,9 +336,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
             float m_run = -INFINITY, l_run = 0.f;   // running maximum and running sum of the row
             bool ok = true;
             for (int j = 0; j < nkb; ++j) {
-                int got = 1;
-                if (lane == 0) got = (!sh->abort && mbar_wait(&sh->s_ready, (uint32_t)j & 1u)) ? 1 : 0;
-                got = __shfl_sync(0xffffffffu, got, 0);
+                const bool got = !sh->abort && mbar_wait(&sh->s_ready, (uint32_t)j & 1u);   // every lane waits: no exchange
                 if (!got) {
                     ok = false;
                     sh->abort = 1;
