@@ -473,13 +473,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) attention_tc_kernel(cons
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&sh->p_ready);
+                if (elect_one()) mbar_arrive(&sh->p_ready);
                 if (tid == 0) AT_STAMP(33 + 4 * (j & 3));
             }
             // ---- epilogue: O / row sum -> fp16 -> global
-            int fin = 1;
-            if (lane == 0) fin = (ok && !sh->abort && mbar_wait(&sh->o_done, 0)) ? 1 : 0;
-            fin = __shfl_sync(0xffffffffu, fin, 0);
+            const bool fin = ok && !sh->abort && mbar_wait(&sh->o_done, 0);
             tc_fence_after();
             if (tid == 0) AT_STAMP(50);
             if (fin) {
