@@ -399,17 +399,13 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             uint32_t phf = 0;
             for (int it = m; it < n_items; it += kMovers) {
                 if (sh->abort) break;
-                int got = 1;
-                if (lane == 1) {
-                    got = mbar_wait(&sh->full[fb], phf);
-                    // the tensor-memory slot: the chunk a_slots before this one must be done
-                    // (with as many slots as stages the producer has already waited for that chunk)
-                    if (got && RA < DB && it >= RA) {
-                        const int prev = it - RA;
-                        got = mbar_wait(&sh->done[prev % DB], (uint32_t)(prev / DB) & 1u);
-                    }
+                bool got = mbar_wait(&sh->full[fb], phf);   // every lane waits: no exchange
+                // the tensor-memory slot: the chunk a_slots before this one must be done
+                // (with as many slots as stages the producer has already waited for that chunk)
+                if (got && RA < DB && it >= RA) {
+                    const int prev = it - RA;
+                    got = mbar_wait(&sh->done[prev % DB], (uint32_t)(prev / DB) & 1u);
                 }
-                got = __shfl_sync(0xffffffffu, got, 1);
                 if (lane == 0 && it < 64) ET_STAMP(700 + it);
                 if (!got) {
                     if (lane == 0) atomicExch(p.err, 12);
@@ -472,12 +468,8 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                             break;
                         }
                         // a_ready implies full: the movers waited for the chunk's TMA before copying. Lane 1 polls.
-                        int got = 1;
-                        if (lane == 1) {
-                            got = mbar_wait(&sh->a_ready[a], pha);
-                            if (w == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(500 + tl * p.k_chunks + kc);
-                        }
-                        got = __shfl_sync(0xffffffffu, got, 1);
+                        const bool got = mbar_wait(&sh->a_ready[a], pha);   // every lane waits: no exchange
+                        if (w == 0 && lane == 1 && tl * p.k_chunks + kc < 64) ET_STAMP(500 + tl * p.k_chunks + kc);
                         if (!got) {
                             if (lane == 0) atomicExch(p.err, 13);
                             sh->abort = 1;
@@ -522,9 +514,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 // tile's 32-column units in turn: TMEM -> registers -> bias / GELU (or a fused LayerNorm mode) -> fp16
                 // -> the warp's own swizzled buffer -> TMA store.
                 if (ok) {
-                    int fin = 1;
-                    if (lane == 1) fin = mbar_wait(&sh->acc_done, (uint32_t)tl & 1u);
-                    fin = __shfl_sync(0xffffffffu, fin, 1);
+                    const bool fin = mbar_wait(&sh->acc_done, (uint32_t)tl & 1u);
                     if (!fin) {
                         if (lane == 0) atomicExch(p.err, 14);
                         sh->abort = 1;
