@@ -337,10 +337,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             for (int kc = 0; kc < p.k_chunks; ++kc) {
                 const uint2 d = dnext;
                 if (lane == 0 && kc + 1 < p.k_chunks) dnext = __ldg(gdir + kc + 1);
-                int go = 1;
-                if (lane == 1)
-                    go = (!sh->abort && mbar_wait(&sh->done[bs], phb ^ 1u)) ? 1 : 0;
-                go = __shfl_sync(0xffffffffu, go, 1);
+                const bool go = !sh->abort && mbar_wait(&sh->done[bs], phb ^ 1u);   // every lane waits: no exchange
                 if (lane == 0 && issued < 64) ET_STAMP(900 + issued);
                 if (!go) {
                     if (lane == 0 && !sh->abort) {
