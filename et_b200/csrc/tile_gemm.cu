@@ -337,7 +337,9 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             for (int kc = 0; kc < p.k_chunks; ++kc) {
                 const uint2 d = dnext;
                 if (lane == 0 && kc + 1 < p.k_chunks) dnext = __ldg(gdir + kc + 1);
-                const bool go = !sh->abort && mbar_wait(&sh->done[bs], phb ^ 1u);   // every lane waits: no exchange
+                // every lane waits: no exchange. (No role reads the abort flag in its loop: a role whose partner has given up
+                // finds out when its own bounded wait runs out.)
+                const bool go = mbar_wait(&sh->done[bs], phb ^ 1u);
                 if (lane == 0 && issued < 64) ET_STAMP(900 + issued);
                 if (!go) {
                     if (lane == 0 && !sh->abort) {
@@ -395,7 +397,6 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             int bs = m % DB, a = m % RA, fb = m;
             uint32_t phf = 0;
             for (int it = m; it < n_items; it += kMovers) {
-                if (sh->abort) break;
                 bool got = mbar_wait(&sh->full[fb], phf);   // every lane waits: no exchange
                 // the tensor-memory slot: the chunk a_slots before this one must be done
                 // (with as many slots as stages the producer has already waited for that chunk)
@@ -459,11 +460,6 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 tc_fence_after();
                 if (issuer) {
                     for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
-                        if (sh->abort) {
-                            sh->issuer_abort[tl & 1] = 1;
-                            ok = false;
-                            break;
-                        }
                         // a_ready implies full: the movers waited for the chunk's TMA before copying. Lane 1 polls.
                         const bool got = mbar_wait(&sh->a_ready[a], pha);   // every lane waits: no exchange
                         if (w == 0 && lane == 1 && tl * p.k_chunks + kc < 64) ET_STAMP(500 + tl * p.k_chunks + kc);
