@@ -44,7 +44,7 @@ LOG2E = 1.4426950408889634
 # DRAM traffic of the dominant kernel from its ncu capture (profiles/): bytes per launch divided by the
 # algorithmic bytes of that launch (activations once, packed weight once, output once). Used to scale the
 # algorithmic bytes of the bench's launches; None where no capture exists.
-NCU_TRAFFIC_RATIO = {"tile_gemm_kernel": 1.0, "source": "profiles/tile_gemm_kernel_T16384_K768_N3072_s75.md: 26.4 MB read "
+NCU_TRAFFIC_RATIO = {"tile_gemm_kernel": 1.0, "source": "profiles/tile_gemm_kernel_T16384_K1024_N4096_s80.md: 35.3 MB read "
                      "= activations + packed weight; writes = the output"}
 
 
