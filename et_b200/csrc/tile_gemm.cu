@@ -17,7 +17,7 @@
 //     cp.async.bulk brings a block into shared memory. The sparsity pattern is kept exactly.
 //   * Persistent CTAs (grid = min(tiles, SMs)); one chunk counter runs on across a CTA's tiles and indexes a ring
 //     of 2-4 shared-memory stages (activations + weight block) and a ring of TMEM A slots. One barrier hop per
-//     role and chunk: producer waits done -> TMA; mover waits full -> tcgen05.cp -> commit a_ready; issuers wait
+//     role and chunk: producer waits done -> TMA; mover waits full -> tcgen05.cp -> arrive a_ready; issuers wait
 //     a_ready -> UMMAs -> commit done. (Every asynchronous operation costs the issuing warp 100-250 clocks, so
 //     the hops per chunk are what the loop time is made of.)
 //   * Epilogue, warp by warp, by sixteen warps (the eight issuers and eight helpers that sleep on a hardware
@@ -111,7 +111,7 @@ __device__ __forceinline__ half2 gelu_tanh_h2(half2 x) {
 struct Shared {
     uint64_t full[kMaxRing];      // [chunk % FB, FB even]  the chunk's activations and weight block have landed (TMA)
     uint64_t done[kMaxRing];      // [chunk % stages]  every issuer's UMMAs on the chunk have completed (8 commits)
-    uint64_t a_ready[kMaxRing];   // [chunk % a_slots] the chunk's activations are in tensor memory (mover commit)
+    uint64_t a_ready[kMaxRing];   // [chunk % a_slots] the copies of the chunk's activations to tensor memory have been issued (mover arrive)
     uint64_t acc_done;            // 8 issuer commits after a tile's last chunk
     uint32_t tmem_base;
     volatile int abort;            // any role gave up: everybody winds down
@@ -418,7 +418,10 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     for (int sl = 0; sl < kSlices; ++sl)
                         tc_cp_128x256b(ta + sl * 8,
                                        make_smem_desc(xa + (sl >> 2) * kPanelBytes + (sl & 3) * 32, 16, 1024, 2));
-                    umma_commit(&sh->a_ready[a]);
+                    // "issued", not "completed": tcgen05 operations execute in issue order, and the fences on either
+                    // side of the barrier carry that order to the issuers, whose UMMAs then queue behind these copies
+                    tc_fence_before();
+                    mbar_arrive(&sh->a_ready[a]);
                     if (it < 64) ET_STAMP(300 + it);
                 }
                 __syncwarp();
