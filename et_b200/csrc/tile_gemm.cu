@@ -15,14 +15,18 @@
 //   * The weight is re-packed once, on the host, into a stream of blocks, one per (block-row chunk,
 //     128-wide K chunk): a per-warp issue list followed by the tiles already in UMMA layout. One
 //     cp.async.bulk brings a block into shared memory. The sparsity pattern is kept exactly.
-//   * Persistent CTAs (grid = min(tiles, SMs)); one chunk counter runs on across a CTA's tiles and indexes a ring
-//     of 2-4 shared-memory stages (activations + weight block) and a ring of TMEM A slots. One barrier hop per
-//     role and chunk: producer waits done -> TMA; mover waits full -> tcgen05.cp -> arrive a_ready; issuers wait
-//     a_ready -> UMMAs -> commit done. (Every asynchronous operation costs the issuing warp 100-250 clocks, so
-//     the hops per chunk are what the loop time is made of.)
+//   * Persistent CTAs (grid = min(tiles, SMs)); one chunk counter runs on across a CTA's tiles and indexes three
+//     rings, one per resource, because the operands live for different times: shared-memory slots for activations
+//     (free once copied on to tensor memory), shared-memory slots for weight blocks (free once their UMMAs have
+//     completed), tensor-memory A slots (free once the UMMAs that read them have been issued: tcgen05 operations
+//     execute in issue order). Roles: warp 0 copies activations, warp 1 weight blocks, warps 2-3 move activations
+//     to tensor memory, warps 4-11 issue UMMAs. (Every asynchronous operation costs the issuing warp 100-250
+//     clocks, so the hops per chunk are what the loop time is made of.)
 //   * Epilogue, warp by warp, by sixteen warps (the eight issuers and eight helpers that sleep on a hardware
 //     barrier during the main loop): tcgen05.ld, + bias, optional GELU, fp16, staged in the warp's own
 //     64-byte-swizzled 32 x 32 buffer and written with one TMA store (rows beyond T and columns beyond N are clipped).
+//   * Every wait is executed by all lanes of the waiting warp (no polling lane and shuffle), and no role reads the
+//     CTA's abort flag inside its loop: both were measured to cost ~10 % and ~3 % of the kernel's time.
 // Every mbarrier wait is bounded; a wait that gives up records a code in the error word, the CTA
 // stops issuing, frees its tensor memory and returns.
 #include <algorithm>
@@ -50,8 +54,10 @@ constexpr int kSlotCols = kKC / 2;  // TMEM columns of one A slot
 constexpr int kMaxRing = 6;           // barriers per ring
 constexpr int kIssuers = 8;         // UMMA-issuing warps; they also take a share of every epilogue
 constexpr int kHelpers = 8;         // warps that only work in the epilogue (asleep on a hardware barrier otherwise)
+constexpr int kProducers = 2;       // warp 0 copies activations, warp 1 weight blocks
 constexpr int kMovers = 2;          // tcgen05.cp-issuing warps, taking chunks in turn
-constexpr int kFirstIssuer = 1 + kMovers;
+constexpr int kFirstMover = kProducers;
+constexpr int kFirstIssuer = kFirstMover + kMovers;
 constexpr int kFirstHelper = kFirstIssuer + kIssuers;
 constexpr int kEpiWarps = kIssuers + kHelpers;
 constexpr int kEpiPerQuarter = kEpiWarps / 4;   // warps that share the 32 rows of a tensor-memory lane quarter
@@ -70,7 +76,7 @@ struct GemmParams {
     const uint8_t* stream;   // packed blocks
     half* Y;
     const half* bias;
-    int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, stages, a_slots, gelu;
+    int T, N, k_chunks, n_chunks, n_tiles, nb, stage_b_bytes, nx, nw, a_slots, gelu;
     int* err;
     uint2 first[kDirInParams];   // dir[chunk][0] for chunk < kDirInParams: no global load before the first TMA
     GemmFusion fz;           // LayerNorm folded into the epilogue (modes 1-3 of the kernel template)
@@ -109,9 +115,15 @@ __device__ __forceinline__ half2 gelu_tanh_h2(half2 x) {
 }
 
 struct Shared {
-    uint64_t full[kMaxRing];      // [chunk % FB, FB even]  the chunk's activations and weight block have landed (TMA)
-    uint64_t done[kMaxRing];      // [chunk % stages]  every issuer's UMMAs on the chunk have completed (8 commits)
-    uint64_t a_ready[kMaxRing];   // [chunk % a_slots] the copies of the chunk's activations to tensor memory have been issued (mover arrive)
+    // Barrier rings (a parity wait is only safe for a waiter that has seen the barrier's previous phase complete and
+    // cannot be a whole phase late, which fixes each ring's length):
+    uint64_t full_x[kMaxRing];    // [chunk % FX]  the chunk's activations have landed (TMA); FX = nx, doubled when odd, so
+                                  //               that a barrier always falls to the same one of the two movers
+    uint64_t full_w[kMaxRing];    // [chunk % FW]  the chunk's weight block has landed (bulk copy); FW from nw likewise
+    uint64_t a_ready[kMaxRing];   // [chunk % kMaxRing]  the chunk's activations are in tensor memory (mover commit): read by
+                                  //               the issuers, and by the activation producer as "shared-memory slot free"
+    uint64_t a_issued[kMaxRing];  // [chunk % a_slots]  every issuer has issued (not completed) its UMMAs on the chunk
+    uint64_t done[kMaxRing];      // [chunk % nw]  every issuer's UMMAs on the chunk have completed (8 commits)
     uint64_t acc_done;            // 8 issuer commits after a tile's last chunk
     uint32_t tmem_base;
     volatile int abort;            // any role gave up: everybody winds down
@@ -268,33 +280,29 @@ __device__ __forceinline__ void epi_fused(const uint32_t (&acc)[32], const uint3
 }
 
 // Persistent: CTA c processes tiles c, c + gridDim.x, ... (tile = slab * n_chunks + chunk, so CTAs that run
-// together share activations in L2). One chunk counter runs on across tiles and indexes two rings:
-//   * `stages` shared-memory stages (32 KB of activations + the weight block), free when the chunk's UMMAs
-//     have completed (they read the tiles there);
-//   * a_slots <= stages tensor-memory slots for the A operand, free when the chunk a_slots before is done,
-//     which the movers read from the `done` barriers with that lag.
-// Every role does as few serial barrier operations per chunk as possible: on this part a wait on a completed
-// mbarrier, a tcgen05.cp or a TMA issue each cost a warp 100-250 clocks, and the chunk period is the longest
-// such chain (a version with a separate, earlier-freed activation ring needed a second wait per chunk in the
-// producer and a second commit in the movers and was 20-50 % slower).
-// While the issuer warps convert and store one tile, the producer and the movers stage the next tile's chunks.
+// together share activations in L2). One chunk counter runs on across tiles and indexes three rings:
+//   * nx shared-memory slots of 32 KB for the activations of a chunk, free as soon as the movers' tcgen05.cp of the
+//     chunk have completed (the movers' one commit per chunk, `a_ready`, is read by the issuers and by the
+//     activation producer);
+//   * nw shared-memory slots for the weight block of a chunk, free when the chunk's UMMAs have completed (`done`);
+//   * a_slots tensor-memory slots for the A operand, free when the UMMAs of the chunk a_slots earlier have been
+//     issued (`a_issued`).
+// What bounds the chunk period is bytes in flight per clock of lifetime; each operand gets the slots its own
+// lifetime needs. Every role does as few serial barrier operations per chunk as possible: on this part a wait on a
+// completed mbarrier, a tcgen05.cp or a TMA issue each cost a warp 100-250 clocks.
+// While the sixteen epilogue warps convert and store one tile, the producers and the movers stage the next tile's
+// first chunks.
 template <bool kGelu, int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmY,
                  const __grid_constant__ GemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int DB = p.stages, RA = p.a_slots;
-    // The `full` barriers form a ring of even length (the stages, twice over when their number is odd): a parity wait
-    // is only safe for a waiter that has seen the barrier's previous phase complete, and the two movers take chunks
-    // in turn, so every barrier must always fall to the same mover. (With three barriers for three stages a mover
-    // that found chunk c+1 landed before chunk c went on to chunk c+3, read the stale parity of the barrier that
-    // chunk c had yet to complete, and copied the slot early.)
-    const int FB = (DB & 1) ? 2 * DB : DB;
-    const int slot_bytes = kXStageBytes + p.stage_b_bytes;   // multiple of 1024: activations, then the weight block
-    uint8_t* const xbase = smem;
-    uint8_t* const bbase = smem + kXStageBytes;
-    uint8_t* const epi = smem + (size_t)DB * slot_bytes;               // 16 warps x 2 KB
+    const int NX = p.nx, NW = p.nw, RA = p.a_slots;
+    const int FX = (NX & 1) ? 2 * NX : NX, FW = (NW & 1) ? 2 * NW : NW;
+    uint8_t* const xring = smem;                                       // NX x 32 KB of activations
+    uint8_t* const wring = smem + (size_t)NX * kXStageBytes;           // NW weight blocks
+    uint8_t* const epi = wring + (size_t)NW * p.stage_b_bytes;         // 16 warps x 2 KB
     Shared* sh = reinterpret_cast<Shared*>(epi + kEpiWarps * kUnitBytes);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = gridDim.x;
@@ -306,40 +314,37 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     // another stream (another batch in flight) could use.
 
     if (warp == 0) {
-        // ---------------- producer warp: lane 0 issues the copies, lane 1 polls (a wait by the thread that has
+        // ---------------- activation producer: lane 0 issues the copies, lane 1 polls (a wait by the thread that has
         // just issued a bulk copy costs several hundred clocks)
-        if (lane < kMaxRing) mbar_init(&sh->full[lane], 1);
-        else if (lane < 2 * kMaxRing) mbar_init(&sh->done[lane - kMaxRing], kIssuers);
+        if (lane < kMaxRing) mbar_init(&sh->full_x[lane], 1);
+        else if (lane < 2 * kMaxRing) mbar_init(&sh->full_w[lane - kMaxRing], 1);
         else if (lane < 3 * kMaxRing) mbar_init(&sh->a_ready[lane - 2 * kMaxRing], 1);
-        else if (lane == 3 * kMaxRing) mbar_init(&sh->acc_done, kIssuers);
-        if (lane <= 3 * kMaxRing) fence_mbar_init();
+        else if (lane < 4 * kMaxRing) mbar_init(&sh->a_issued[lane - 3 * kMaxRing], kIssuers);
+        else if (lane < 5 * kMaxRing) mbar_init(&sh->done[lane - 4 * kMaxRing], kIssuers);
+        else if (lane == 5 * kMaxRing) mbar_init(&sh->acc_done, kIssuers);
+        static_assert(5 * kMaxRing < 32, "one lane per barrier");
+        if (lane <= 5 * kMaxRing) fence_mbar_init();
         if (lane == 0) {
             sh->abort = 0;
             sh->issuer_abort[0] = 0;
             sh->issuer_abort[1] = 0;
         }
         __syncwarp();
+        named_barrier_arrive(4, 64);         // the weight producer may start
         named_barrier_arrive(2, kThreads);   // barriers are initialised: release the other warps
         if (lane == 0) ET_STAMP(8);
         // Everything above touched only this kernel's own resources. The activations may still be in the making:
         // wait for the preceding kernels before the first copy (lane 0 issues them all).
         if (lane == 0) pdl_wait();
-        int issued = 0, bs = 0, fb = 0;
-        uint32_t phb = 0;
+        int issued = 0, xs = 0, fx = 0, ar = 0;
+        uint32_t pha = 0;
         bool alive = true;
         for (int tl = 0; tl < my_tiles && alive; ++tl) {
             const int tile = (int)blockIdx.x + tl * G;
-            const int slab = tile / p.n_chunks, chunk = tile - slab * p.n_chunks;
-            const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
-            // directory entries: the first one of the first tile comes from the kernel parameters, the others are
-            // fetched one chunk ahead
-            uint2 dnext = (tl == 0 && chunk < kDirInParams) ? p.first[chunk] : (lane == 0 ? __ldg(gdir) : make_uint2(0, 0));
+            const int slab = tile / p.n_chunks;
             for (int kc = 0; kc < p.k_chunks; ++kc) {
-                const uint2 d = dnext;
-                if (lane == 0 && kc + 1 < p.k_chunks) dnext = __ldg(gdir + kc + 1);
-                // every lane waits: no exchange. (No role reads the abort flag in its loop: a role whose partner has given up
-                // finds out when its own bounded wait runs out.)
-                const bool go = mbar_wait(&sh->done[bs], phb ^ 1u);
+                // the slot is free when the chunk NX before this one has been copied on to tensor memory
+                const bool go = issued < NX || mbar_wait(&sh->a_ready[ar], pha);
                 if (lane == 0 && issued < 64) ET_STAMP(900 + issued);
                 if (!go) {
                     if (lane == 0 && !sh->abort) {
@@ -350,29 +355,69 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     break;
                 }
                 if (lane == 0) {
-                    const uint32_t bbytes = d.y * 16u;
-                    mbar_expect_tx(&sh->full[fb], kXStageBytes + bbytes);
-                    tma_load_3d(xbase + (size_t)bs * slot_bytes, &tmX, 0, slab * kSlab, kc * (kKC / kPanel),
-                                &sh->full[fb]);   // both panels, one op
-                    bulk_load(bbase + (size_t)bs * slot_bytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full[fb]);
+                    mbar_expect_tx(&sh->full_x[fx], kXStageBytes);
+                    tma_load_3d(xring + (size_t)xs * kXStageBytes, &tmX, 0, slab * kSlab, kc * (kKC / kPanel),
+                                &sh->full_x[fx]);   // both panels, one op
                     if (issued < 64) ET_STAMP(100 + issued);
                 }
+                if (issued >= NX && ++ar == kMaxRing) { ar = 0; pha ^= 1u; }
                 ++issued;
-                if (++fb == FB) fb = 0;
-                if (++bs == DB) { bs = 0; phb ^= 1u; }
+                if (++fx == FX) fx = 0;
+                if (++xs == NX) xs = 0;
             }
         }
         // Leaving early: wait (bounded) for the copies still in flight before the CTA exits.
         if (lane == 1 && sh->abort)
-            for (int kk = issued > DB ? issued - DB : 0; kk < issued; ++kk)
-                mbar_wait(&sh->full[kk % FB], (uint32_t)(kk / FB) & 1u);
+            for (int kk = issued > NX ? issued - NX : 0; kk < issued; ++kk)
+                mbar_wait(&sh->full_x[kk % FX], (uint32_t)(kk / FX) & 1u);
+    } else if (warp == 1) {
+        // ---------------- weight producer: the packed weight does not depend on the preceding kernel, so these copies
+        // start as soon as the barriers exist. A slot is free when the UMMAs that read it have completed.
+        named_barrier_sync(4, 64);
+        named_barrier_arrive(2, kThreads);
+        int issued = 0, ws = 0, fw = 0;
+        uint32_t phw = 0;
+        bool alive = true;
+        for (int tl = 0; tl < my_tiles && alive; ++tl) {
+            const int tile = (int)blockIdx.x + tl * G;
+            const int chunk = tile % p.n_chunks;
+            const uint2* gdir = p.dir + (size_t)chunk * p.k_chunks;
+            // directory entries: the first one of the first tile comes from the kernel parameters, the others are
+            // fetched one chunk ahead
+            uint2 dnext = (tl == 0 && chunk < kDirInParams) ? p.first[chunk] : (lane == 0 ? __ldg(gdir) : make_uint2(0, 0));
+            for (int kc = 0; kc < p.k_chunks; ++kc) {
+                const uint2 d = dnext;
+                if (lane == 0 && kc + 1 < p.k_chunks) dnext = __ldg(gdir + kc + 1);
+                const bool go = mbar_wait(&sh->done[ws], phw ^ 1u);
+                if (!go) {
+                    if (lane == 0 && !sh->abort) {
+                        atomicExch(p.err, 15);
+                        sh->abort = 1;
+                    }
+                    alive = false;
+                    break;
+                }
+                if (lane == 0) {
+                    const uint32_t bbytes = d.y * 16u;
+                    mbar_expect_tx(&sh->full_w[fw], bbytes);
+                    bulk_load(wring + (size_t)ws * p.stage_b_bytes, p.stream + (size_t)d.x * 16u, bbytes, &sh->full_w[fw]);
+                    if (issued < 64) ET_STAMP(1100 + issued);
+                }
+                ++issued;
+                if (++fw == FW) fw = 0;
+                if (++ws == NW) { ws = 0; phw ^= 1u; }
+            }
+        }
+        if (lane == 1 && sh->abort)
+            for (int kk = issued > NW ? issued - NW : 0; kk < issued; ++kk)
+                mbar_wait(&sh->full_w[kk % FW], (uint32_t)(kk / FW) & 1u);
     } else {
-        if (warp == 1) {
+        if (warp == kFirstMover) {
             tmem_alloc(&sh->tmem_base, 512);
             tmem_relinquish();
         }
         tc_fence_before();
-        named_barrier_sync(1, kThreads - 32);   // all but the producer: the tensor-memory base is visible
+        named_barrier_sync(1, kThreads - 32 * kProducers);   // all but the producers: the tensor-memory base is visible
         tc_fence_after();
         const uint32_t tmem = sh->tmem_base;
         // Accumulators start at zero: block-rows without tiles are legal and every UMMA accumulates. (After
@@ -384,26 +429,25 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             tmem_st_wait();
         }
         tc_fence_before();
-        named_barrier_sync(2, kThreads);        // + the producer's arrive: mbarriers are initialised
+        named_barrier_sync(2, kThreads);        // + the producers' arrives: mbarriers are initialised
         tc_fence_after();
-        if (tid == 32) ET_STAMP(2);
+        if (tid == 32 * kFirstMover) ET_STAMP(2);
         const int n_items = my_tiles * p.k_chunks;
 
         if (warp < kFirstIssuer) {
             // ---------------- movers: shared memory -> tensor memory copy of the A operand. The mover warps take
-            // chunks in turn (a warp needs ~1500 clocks per chunk: two barrier waits, eight tcgen05.cp, two
-            // commits); lane 1 polls, lane 0 issues and commits.
-            const int m = warp - 1;
-            int bs = m % DB, a = m % RA, fb = m;
-            uint32_t phf = 0;
+            // chunks in turn; lane 1 polls, lane 0 issues and commits. The tensor-memory slot is free as soon as the
+            // issuers have ISSUED the UMMAs of the chunk a_slots earlier: tcgen05 operations execute in issue order
+            // (the order across threads being established by the fence + barrier pair), so the copy cannot overtake
+            // the UMMAs that still read the slot, and the hop "UMMAs completed -> seen by the mover" (~500 clocks)
+            // leaves the slot's cycle. The one commit per chunk tells the issuers that A is in place and the
+            // activation producer that the shared-memory slot may be overwritten.
+            const int m = warp - kFirstMover;
+            int xs = m % NX, a = m % RA, fx = m, fw = m, ar = m;
+            uint32_t phx = 0, phw = 0;
             for (int it = m; it < n_items; it += kMovers) {
-                bool got = mbar_wait(&sh->full[fb], phf);   // every lane waits: no exchange
-                // the tensor-memory slot: the chunk a_slots before this one must be done
-                // (with as many slots as stages the producer has already waited for that chunk)
-                if (got && RA < DB && it >= RA) {
-                    const int prev = it - RA;
-                    got = mbar_wait(&sh->done[prev % DB], (uint32_t)(prev / DB) & 1u);
-                }
+                bool got = mbar_wait(&sh->full_x[fx], phx);
+                if (got && it >= RA) got = mbar_wait(&sh->a_issued[a], (uint32_t)(it / RA - 1) & 1u);
                 if (lane == 0 && it < 64) ET_STAMP(700 + it);
                 if (!got) {
                     if (lane == 0) atomicExch(p.err, 12);
@@ -412,23 +456,34 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 }
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint32_t xa = smem_u32(xbase + (size_t)bs * slot_bytes);
+                    const uint32_t xa = smem_u32(xring + (size_t)xs * kXStageBytes);
                     const uint32_t ta = tmem + a_col0 + a * kSlotCols;
 #pragma unroll
                     for (int sl = 0; sl < kSlices; ++sl)
                         tc_cp_128x256b(ta + sl * 8,
                                        make_smem_desc(xa + (sl >> 2) * kPanelBytes + (sl & 3) * 32, 16, 1024, 2));
-                    // "issued", not "completed": tcgen05 operations execute in issue order, and the fences on either
-                    // side of the barrier carry that order to the issuers, whose UMMAs then queue behind these copies
-                    tc_fence_before();
-                    mbar_arrive(&sh->a_ready[a]);
+                }
+                // The issuers take "A is in place" to mean "the chunk is in place": the commit waits for the weight block,
+                // whose copy started later (its slot is free only when UMMAs have completed); the tcgen05.cp run meanwhile.
+                got = mbar_wait(&sh->full_w[fw], phw);
+                if (!got) {
+                    if (lane == 0) atomicExch(p.err, 12);
+                    sh->abort = 1;
+                    break;
+                }
+                if (lane == 0) {
+                    umma_commit(&sh->a_ready[ar]);
                     if (it < 64) ET_STAMP(300 + it);
                 }
                 __syncwarp();
-                bs = (bs + kMovers) % DB;
-                fb += kMovers;
-                if (fb >= FB) { fb -= FB; phf ^= 1u; }
+                xs = (xs + kMovers) % NX;
                 a = (a + kMovers) % RA;
+                fx += kMovers;
+                if (fx >= FX) { fx -= FX; phx ^= 1u; }
+                fw += kMovers;
+                if (fw >= FW) { fw -= FW; phw ^= 1u; }
+                ar += kMovers;
+                if (ar >= kMaxRing) ar -= kMaxRing;
             }
         } else {
             // ---------------- issuers (one UMMA per kept tile, A from tensor memory) and epilogue helpers. All sixteen
@@ -445,7 +500,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             // this warp's output staging: 32 rows x 32 columns (64-byte rows, 64-byte swizzle)
             uint8_t* const buf = epi + (size_t)w * kUnitBytes;
             bool ok = true;
-            int bs = 0, a = 0;
+            int ws = 0, a = 0, ar = 0;
             uint32_t pha = 0;
             for (int tl = 0; tl < my_tiles; ++tl) {
                 const int tile = (int)blockIdx.x + tl * G;
@@ -463,9 +518,8 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                 tc_fence_after();
                 if (issuer) {
                     for (int kc = 0; kc < p.k_chunks && ok; ++kc) {
-                        // a_ready implies full: the movers waited for the chunk's TMA before copying. Lane 1 polls.
-                        const bool got = mbar_wait(&sh->a_ready[a], pha);   // every lane waits: no exchange
-                        if (w == 0 && lane == 1 && tl * p.k_chunks + kc < 64) ET_STAMP(500 + tl * p.k_chunks + kc);
+                        // a_ready implies that the weight block has landed too: the movers waited for both copies.
+                        const bool got = mbar_wait(&sh->a_ready[ar], pha);
                         if (!got) {
                             if (lane == 0) atomicExch(p.err, 13);
                             sh->abort = 1;
@@ -474,7 +528,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                             break;
                         }
                         tc_fence_after();
-                        const uint8_t* blk = bbase + (size_t)bs * slot_bytes;
+                        const uint8_t* blk = wring + (size_t)ws * p.stage_b_bytes;
                         const uint32_t hw = reinterpret_cast<const uint32_t*>(blk)[w];
                         const int e0 = hw & 0xffff, ne = hw >> 16;
                         const uint32_t n_entries = reinterpret_cast<const uint32_t*>(blk)[8];
@@ -487,11 +541,17 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                             if (elect_one())
                                 umma_f16_ts(tmem + en.z, abuf + en.y, b_desc0 | (uint64_t)((tiles16 + en.x) & 0x3fff), en.w, 1u);
                         }
-                        if (elect_one()) umma_commit(&sh->done[bs]);
+                        if (elect_one()) {
+                            // issued: the tensor-memory slot may be refilled behind these UMMAs; completed: the weight slot
+                            tc_fence_before();
+                            mbar_arrive(&sh->a_issued[a]);
+                            umma_commit(&sh->done[ws]);
+                        }
                         if (w == 0 && lane == 0 && tl * p.k_chunks + kc < 64) ET_STAMP(600 + tl * p.k_chunks + kc);
                         __syncwarp();
-                        if (++bs == DB) bs = 0;
-                        if (++a == RA) { a = 0; pha ^= 1u; }
+                        if (++ws == NW) ws = 0;
+                        if (++a == RA) a = 0;
+                        if (++ar == kMaxRing) { ar = 0; pha ^= 1u; }
                     }
                     if (elect_one()) umma_commit(&sh->acc_done);
                     __syncwarp();
@@ -589,7 +649,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     if (tid == 0) ET_STAMP(4);
-    if (warp == 1) tmem_dealloc(sh->tmem_base, 512);
+    if (warp == kFirstMover) tmem_dealloc(sh->tmem_base, 512);
 }
 
 }  // namespace
@@ -597,7 +657,7 @@ tile_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 // --------------------------------------------------------------------------------- host side
 
 struct TileWeight {
-    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, stages = 0, a_slots = 0;
+    int K = 0, N = 0, nb = 0, n_chunks = 0, k_chunks = 0, stage_b_bytes = 0, nx = 0, nw = 0, a_slots = 0;
     int tiles_per_cta = 1;   // > 1 when packed for SM time: a CTA takes that many tiles even when SMs are free
     long ntile = 0;
     int size_hint = 0;
@@ -614,22 +674,25 @@ struct TileWeight {
     size_t stream_bytes = 0;
 };
 
-// Ring depth for a chunk shape: as many stages as shared memory holds (at most four: beyond that the ring is
-// no longer what bounds the chunk period), with two epilogue staging buffers per warp when they do not cost a
-// stage. A stage goes round in ~4000 clocks (TMA, tcgen05.cp, UMMAs, and the polls between them), a
-// tensor-memory slot in ~2000.
-struct RingShape { int stages, a_slots; double period; };
+// Ring depths for a chunk shape. The operands live for different times, so each has its own ring: an activation
+// slot (32 KB) goes round in ~2700 clocks (free when copied on to tensor memory -> seen by the producer -> TMA ->
+// landed -> copied), a weight slot in ~2500 (free when its UMMAs have completed -> seen -> bulk copy -> landed ->
+// the issuers reach it), a tensor-memory slot in ~1400 (UMMAs issued -> seen by the mover -> eight tcgen05.cp ->
+// seen by the issuers). The period of a chunk is the largest cycle / depth; shared memory is shared out to make
+// that smallest (at most four slots per ring: beyond that the cycles above no longer bound the period).
+struct RingShape { int nx, nw, a_slots; double period; };
 static RingShape ring_shape(int nb, int stage_b_bytes) {
-    const int tmem_slots = std::min(kMaxRing, (512 - nb * 16) / kSlotCols);
-    const int slot = kXStageBytes + stage_b_bytes;
-    const int avail1 = kSmemMax - 1024 - (int)sizeof(Shared) - kEpiWarps * kUnitBytes;
-    const int cap = 4;   // an odd number of stages uses twice as many `full` barriers
-    static_assert(kMovers == 2 && 2 * 3 <= kMaxRing && cap <= kMaxRing, "the full-barrier ring must fit");
-    RingShape r;
-    r.stages = std::min(cap, avail1 / slot);
-    r.a_slots = std::min(r.stages, tmem_slots);
-    r.period = r.stages >= 1 && r.a_slots >= 1 ? std::max(4000.0 / r.stages, 2000.0 / r.a_slots) : 1e30;
-    return r;
+    const int tmem_slots = std::min(4, (512 - nb * 16) / kSlotCols);
+    const int avail = kSmemMax - 1024 - (int)sizeof(Shared) - kEpiWarps * kUnitBytes;
+    static_assert(kMovers == 2 && 2 * 3 <= kMaxRing && 4 <= kMaxRing, "the full-barrier rings must fit");
+    RingShape best{0, 0, tmem_slots, 1e30};
+    for (int nx = 2; nx <= 4; ++nx)
+        for (int nw = 2; nw <= 4; ++nw) {
+            if (nx * kXStageBytes + nw * stage_b_bytes > avail || tmem_slots < 1) continue;
+            const double period = std::max({2700.0 / nx, 2500.0 / nw, 1400.0 / tmem_slots});
+            if (period < best.period * 0.999) best = RingShape{nx, nw, tmem_slots, period};
+        }
+    return best;
 }
 // Block-rows per CTA from a model of the persistent kernel: a chunk takes the ring period, or its UMMAs (~10
 // clocks each with eight issuing warps), or its share of L2 bandwidth (~64 bytes per clock per SM), whichever
@@ -656,7 +719,7 @@ static int choose_nb(int n_block_rows, int k_chunks, int size_hint, double densi
                                           tiles_per_chunk + 3.0 * std::sqrt(nbe * kSlices * density * (1.0 - density)));
         const int stage_b = (int)((kHeaderBytes + tiles_max * 528.0 + 1023) / 1024) * 1024;
         const RingShape rs = ring_shape(nbe, stage_b);
-        if (rs.stages < 2 || rs.a_slots < 1) continue;
+        if (rs.nx < 2 || rs.a_slots < 1) continue;
         const long tiles = (long)slabs * ((n_block_rows + nbe - 1) / nbe);
         const double per_cta = (double)((tiles + sms - 1) / sms);
         const double t_chunk = std::max({rs.period, 10.0 * tiles_per_chunk,
@@ -748,9 +811,9 @@ int tile_weight_pack(TileWeight** out, int K, int N, int size_hint, long ntile, 
     w->stage_b_bytes = (int)((max_block + 1023) / 1024 * 1024);
     {
         const RingShape rs = ring_shape(w->nb, w->stage_b_bytes);
-        w->stages = rs.stages; w->a_slots = rs.a_slots;
+        w->nx = rs.nx; w->nw = rs.nw; w->a_slots = rs.a_slots;
     }
-    if (w->stages < 2 || w->a_slots < 1) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
+    if (w->nx < 2 || w->a_slots < 1) { delete w; return fail(ET_ERR_UNSUPPORTED, "tile weight: weight block exceeds shared memory"); }
     w->stream_bytes = stream.size();
 
     cudaError_t e1 = cudaMalloc(&w->d_dir, dir.size() * sizeof(uint2));
@@ -835,10 +898,10 @@ int tile_linear_run(const TileWeight* w, half* Y, const half* X, int T, int gelu
     p.T = T; p.N = w->N; p.k_chunks = w->k_chunks; p.nb = w->nb;
     p.n_chunks = w->n_chunks;
     p.n_tiles = ((T + kSlab - 1) / kSlab) * w->n_chunks;
-    p.stage_b_bytes = w->stage_b_bytes; p.stages = w->stages; p.a_slots = w->a_slots; p.gelu = gelu; p.err = w->d_err;
+    p.stage_b_bytes = w->stage_b_bytes; p.nx = w->nx; p.nw = w->nw; p.a_slots = w->a_slots; p.gelu = gelu; p.err = w->d_err;
     p.prof = g_prof;
     for (size_t c = 0; c < w->h_first.size(); ++c) p.first[c] = w->h_first[c];
-    const size_t smem = (size_t)w->stages * (kXStageBytes + w->stage_b_bytes) +
+    const size_t smem = (size_t)w->nx * kXStageBytes + (size_t)w->nw * w->stage_b_bytes +
                         (size_t)kEpiWarps * kUnitBytes + sizeof(Shared) + 1024;
     // Packed for SM time (several batches in flight): a CTA takes several tiles in a row even when SMs are free,
     // so that set-up and pipeline fill are paid once and the next tile's loads run under an epilogue.
@@ -920,7 +983,7 @@ int tile_weight_error(const TileWeight* w, int* code) {
 }
 
 void tile_weight_info(const TileWeight* w, int* info) {
-    info[0] = w->nb; info[1] = w->n_chunks; info[2] = w->k_chunks; info[3] = w->stages;
+    info[0] = w->nb; info[1] = w->n_chunks; info[2] = w->k_chunks; info[3] = w->nx;   // activation slots (the weight ring has w->nw, chosen from the same memory)
     info[4] = w->stage_b_bytes; info[5] = (int)std::min<size_t>(w->stream_bytes, 0x7fffffff);
 }
 
